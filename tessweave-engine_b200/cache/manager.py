@@ -66,7 +66,8 @@ class PageGroup:
         self.window = need.window
         shape = (len(entries), num_pages, need.kv_heads, page_size)
         self.k = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
-        self.v = torch.zeros(shape + (need.value_dim,), dtype=dtype, device=device)     # value rows may differ in length
+        # value rows may differ in length; where a position's value is its key the key pages serve as both
+        self.v = self.k if need.values_are_keys else torch.zeros(shape + (need.value_dim,), dtype=dtype, device=device)
         self.refs = [0] * num_pages
         self.free = list(reversed(range(num_pages)))    # pop() hands out low ids first
         self.promised = 0
@@ -78,7 +79,7 @@ class PageGroup:
 
     @property
     def bytes(self) -> int:
-        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+        return (self.k.numel() + (0 if self.v is self.k else self.v.numel())) * self.k.element_size()
 
     def unpromised_free(self) -> int:
         return len(self.free) - self.promised

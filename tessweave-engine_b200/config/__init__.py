@@ -2,8 +2,9 @@
 from .model_config import ConfigError, Qwen2Config
 from .linurax_config import LinuraxConfig
 from .sapatar_config import SapatarConfig
+from .nufatar_config import NufatarConfig
 from .engine_config import EngineConfig
 from .registry import architecture_of, architectures, register_architecture, resolve, resolve_folder
 
-__all__ = ["ConfigError", "Qwen2Config", "LinuraxConfig", "SapatarConfig", "EngineConfig", "architecture_of", "architectures",
+__all__ = ["ConfigError", "Qwen2Config", "LinuraxConfig", "SapatarConfig", "NufatarConfig", "EngineConfig", "architecture_of", "architectures",
            "register_architecture", "resolve", "resolve_folder"]

@@ -9,8 +9,9 @@
 // lo..position of its own request through that request's block table.
 //
 //   kv_head = head / (Hq / Hkv)
-//   score_p = (q . k_p) * scale            p in [lo, position], lo = max(0, position - window + 1)
-//   out     = softmax(score) @ v
+//   score_p = (q . k_p) * scale [+ bias[min(position - p, bias_rows - 1), head]]
+//                                          p in [lo, position], lo = max(0, position - window + 1)
+//   out     = softmax(score) @ v           [the denominator also holds exp(sink[head]): a term without key or value]
 // Reference: flow_engine/model.py:193-200 (mask p <= position), flow_engine/
 // kernels/paged_decode.py:13-43 (online softmax in fp32, GQA head map).
 //
@@ -28,6 +29,7 @@ __global__ void attn_generic_kernel(T* __restrict__ out, int out_stride, const T
                                     const int* __restrict__ seq_slot, const int* __restrict__ block_table,
                                     int table_stride, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                     int Hq, int Hkv, int D, int Dv, int page_size, int num_pages, int window, float scale,
+                                    const float* __restrict__ dist_bias, int bias_rows, const float* __restrict__ sink,
                                     int* status) {
     extern __shared__ float smem[];  // TW_ATTN_WARPS * (Dv + 2)
     tw_grid_wait();
@@ -68,6 +70,7 @@ __global__ void attn_generic_kernel(T* __restrict__ out, int out_stride, const T
             if (d < D) dot += qr[j] * tw_to_float(kr[d]);
         }
         dot = tw_warp_sum(dot) * scale;
+        if (dist_bias) dot += dist_bias[(size_t)min(pos - p, bias_rows - 1) * Hq + head];
         const float m_new = fmaxf(m, dot);
         const float alpha = expf(m - m_new);   // m == -inf gives 0
         const float w = expf(dot - m_new);
@@ -92,6 +95,10 @@ __global__ void attn_generic_kernel(T* __restrict__ out, int out_stride, const T
 #pragma unroll
     for (int w = 0; w < TW_ATTN_WARPS; ++w) M = fmaxf(M, smem[w * (Dv + 2) + Dv]);
     float f[TW_ATTN_WARPS], L = 0.f;
+    if (sink) {
+        M = fmaxf(M, sink[head]);
+        L = expf(sink[head] - M);
+    }
 #pragma unroll
     for (int w = 0; w < TW_ATTN_WARPS; ++w) {
         const float mw = smem[w * (Dv + 2) + Dv];
@@ -110,9 +117,10 @@ __global__ void attn_generic_kernel(T* __restrict__ out, int out_stride, const T
 TW_EXPORT int tw_attn_generic(void* out, int out_stride, const void* q, int q_stride, const int* positions,
                               const int* seq_of_token, const int* seq_slot, const int* block_table, int table_stride,
                               const void* k_cache, const void* v_cache, int n_tokens, int Hq, int Hkv, int D,
-                              int Dv, int page_size, int num_pages, int window, float scale, int dtype, int* status,
-                              cudaStream_t stream) {
+                              int Dv, int page_size, int num_pages, int window, float scale, const float* dist_bias,
+                              int bias_rows, const float* sink, int dtype, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (dist_bias && bias_rows <= 0) return (int)cudaErrorInvalidValue;
     if (D <= 0 || D > 32 * TW_ATTN_MAXR || Dv <= 0 || Dv > 32 * TW_ATTN_MAXR || Hkv <= 0 || Hq % Hkv) return (int)cudaErrorInvalidValue;
     dim3 grid(n_tokens, Hq);
     const size_t smem = (size_t)TW_ATTN_WARPS * (Dv + 2) * sizeof(float);
@@ -120,11 +128,11 @@ TW_EXPORT int tw_attn_generic(void* out, int out_stride, const void* q, int q_st
         tw_launch(attn_generic_kernel<float>, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1, 
             (float*)out, out_stride, (const float*)q, q_stride, positions, seq_of_token, seq_slot, block_table,
             table_stride, (const float*)k_cache, (const float*)v_cache, Hq, Hkv, D, Dv, page_size, num_pages, window, scale,
-            status);
+            dist_bias, bias_rows, sink, status);
     else
         tw_launch(attn_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1, 
             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, positions, seq_of_token, seq_slot,
             block_table, table_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, Hq, Hkv, D, Dv,
-            page_size, num_pages, window, scale, status);
+            page_size, num_pages, window, scale, dist_bias, bias_rows, sink, status);
     return TW_LAUNCH_CHECK();
 }

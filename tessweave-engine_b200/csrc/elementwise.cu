@@ -720,12 +720,13 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
 // ---------------------------------------------------------------------------
 // Rotation of pairs in place, on the first `n_heads` heads of each packed row and the first `rot_dims`
 // values of a head: angle = float(position) * inv_freq[i]; pair i is (2i, 2i+1) when `interleaved`, else
-// (i, i + rot_dims / 2).  The general form of the rotation above, for encodings no fused kernel takes.
+// (i, i + rot_dims / 2); cos and sin are both multiplied by `magnitude`.  The general form of the rotation above, for
+// encodings no fused kernel takes.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void rotate_pairs_kernel(T* __restrict__ rows, int row_stride, const int* __restrict__ positions,
                                     const int* __restrict__ seq_of_token, const float* __restrict__ inv_freq, int n_heads,
-                                    int D, int rot_dims, int interleaved) {
+                                    int D, int rot_dims, int interleaved, float magnitude) {
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int n = blockIdx.x;
@@ -738,6 +739,8 @@ __global__ void rotate_pairs_kernel(T* __restrict__ rows, int row_stride, const 
         const int a = head * D + (interleaved ? 2 * i : i), b = head * D + (interleaved ? 2 * i + 1 : i + half);
         float sn, cs;
         sincosf((float)pos * inv_freq[i], &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
         const float u = tw_to_float(row[a]), v = tw_to_float(row[b]);
         row[a] = tw_from_float<T>(u * cs - v * sn);
         row[b] = tw_from_float<T>(v * cs + u * sn);
@@ -746,16 +749,16 @@ __global__ void rotate_pairs_kernel(T* __restrict__ rows, int row_stride, const 
 
 TW_EXPORT int tw_rotate_pairs(void* rows, int row_stride, const int* positions, const int* seq_of_token,
                               const float* inv_freq, int n_tokens, int n_heads, int D, int rot_dims, int interleaved,
-                              int dtype, cudaStream_t stream) {
+                              float magnitude, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || rot_dims < 2) return 0;
     if (rot_dims > D || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
     const int work = n_heads * (rot_dims / 2);
     const dim3 grid(n_tokens, (work + 127) / 128 < 8 ? (work + 127) / 128 : 8);
     if (dtype == TW_F32)
         return tw_launch(rotate_pairs_kernel<float>, grid, dim3(128), 0, stream, 1, (float*)rows, row_stride, positions,
-                         seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved);
+                         seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved, magnitude);
     return tw_launch(rotate_pairs_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, (__nv_bfloat16*)rows, row_stride,
-                     positions, seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved);
+                     positions, seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved, magnitude);
 }
 
 // ---------------------------------------------------------------------------
@@ -950,6 +953,7 @@ __global__ void kv_store_kernel(const T* __restrict__ rows, int stride, int k_co
         const int h = i / Dk, d = i - h * Dk;
         k_cache[(((size_t)page * Hkv + h) * page_size + in_page) * Dk + d] = row[k_col + i];
     }
+    if (!v_cache) return;        // the values are the keys: one set of pages
     for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
         const int h = i / Dv, d = i - h * Dv;
         v_cache[(((size_t)page * Hkv + h) * page_size + in_page) * Dv + d] = row[v_col + i];
@@ -995,4 +999,87 @@ TW_EXPORT int tw_scaled_accumulate(float* acc, void* out, const void* x, float s
                          first, (size_t)count);
     return tw_launch(scaled_accumulate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, acc, (__nv_bfloat16*)out,
                      (const __nv_bfloat16*)x, scale, first, (size_t)count);
+}
+
+// ---------------------------------------------------------------------------
+// resid[n, :] += vec for the first n_rows rows: a learned vector added to every row of the fp32 residual stream.
+// ---------------------------------------------------------------------------
+__global__ void add_row_vector_kernel(float* __restrict__ resid, const float* __restrict__ vec, int width, size_t count) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) resid[i] += vec[i % width];
+}
+
+TW_EXPORT int tw_add_row_vector(float* resid, const float* vec, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    const size_t count = (size_t)n_rows * width;
+    return tw_launch(add_row_vector_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), 0, stream, 1, resid, vec, width, count);
+}
+
+// ---------------------------------------------------------------------------
+// resid += delta in fp32, where delta is a tensor of the activation type or the fp32 slices of a split product
+// (added in slice order first).  For blocks that add a sub-layer's result without a norm behind it.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_delta_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ partial,
+                                 int nsplit, size_t split_stride, size_t count) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float d = 0.f;
+    if (partial) {
+        for (int k = 0; k < nsplit; ++k) d += partial[(size_t)k * split_stride + i];
+    } else {
+        d = tw_to_float(delta[i]);
+    }
+    resid[i] += d;
+}
+
+TW_EXPORT int tw_add_delta(float* resid, const void* delta, const float* partial, int nsplit, long long split_stride,
+                           long long count, int dtype, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const dim3 grid((unsigned)((count + 255) / 256));
+    if (dtype == TW_F32)
+        return tw_launch(add_delta_kernel<float>, grid, dim3(256), 0, stream, 1, resid, (const float*)delta, partial, nsplit,
+                         (size_t)split_stride, (size_t)count);
+    return tw_launch(add_delta_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, resid, (const __nv_bfloat16*)delta, partial,
+                     nsplit, (size_t)split_stride, (size_t)count);
+}
+
+// ---------------------------------------------------------------------------
+// acc[n] = (first ? 0 : acc[n]) + scale * x[n] / sqrt(mean(x[n]^2) + eps) * weight, row by row in fp32; `out` (may be
+// null) receives the new acc in the activation type.  For mixers that normalise each member's result before the sum.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+normed_accumulate_kernel(float* __restrict__ acc, T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ weight,
+                         float eps, float scale, int first, int width) {
+    __shared__ float scratch[33];
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = tw_to_float(x[base + c]);
+        ss += v * v;
+    }
+    ss = tw_block_sum(ss, scratch);
+    const float f = scale / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = (first ? 0.f : acc[base + c]) + tw_to_float(x[base + c]) * f * weight[c];
+        acc[base + c] = v;
+        if (out) out[base + c] = tw_from_float<T>(v);
+    }
+}
+
+TW_EXPORT int tw_normed_accumulate(float* acc, void* out, const void* x, const float* weight, float eps, float scale, int first,
+                                   int n_rows, int width, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    if (dtype == TW_F32)
+        return tw_launch(normed_accumulate_kernel<float>, dim3(n_rows), dim3(256), 0, stream, 1, acc, (float*)out, (const float*)x,
+                         weight, eps, scale, first, width);
+    return tw_launch(normed_accumulate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, 1, acc, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)x, weight, eps, scale, first, width);
 }

@@ -10,6 +10,12 @@
 //                      n likewise with k alone;  o = S^T q,  den = max(|n . q|, e^(-m')) + 1e-6
 //                      i = cap tanh((pi + bi) / cap), f = logsigmoid(cap tanh((pf + bf) / cap)); m is 0 before
 //                      the first token.  n is carried as one more column of S (a value that is always 1).
+//   TW_REC_DELTA       S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q      (the gated delta rule)
+//                      g = exp(-exp(A_h) softplus(d + b)) per head, or per head and key channel, from the projected d;
+//                      beta = sigmoid of a projected number per head.  q and k arrive as fp32 rows that the caller has
+//                      prepared (here: convolved, activated, scaled to unit length); heads of v may share a head of q
+//                      and k (qk_group value heads per q/k head).  The read-out sees the token's own write:
+//                      o = (gS)^T q + u (k . q), so one pass over the column gives (gS)^T k, (gS)^T q and k . q.
 //
 // One block per (head, request, slice of the columns of S): a thread owns a column of S in registers (TW_DK
 // values, a compile-time size; where that size is a multiple of 16 four lanes share a column, a quarter of its key
@@ -30,7 +36,7 @@
 // l + 16, l + 24 of a warp), and their partial outputs are added by two shuffles.
 #define TW_REC_KSPLIT ((TW_DK % 16 == 0) ? 4 : 1)
 
-enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2 };
+enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2, TW_REC_DELTA = 3 };
 
 struct RecArgs {
     float* out;                 // [rows, H * Dv] fp32
@@ -38,9 +44,12 @@ struct RecArgs {
     const void* q; int q_stride;        // rows of q (r), k, v: element type T, column h * D + i inside each
     const void* k; int k_stride;
     const void* v; int v_stride;
-    const float* wpre; int wpre_stride; // wkv: d [rows, H * Dk] fp32;  mlstm: [rows, 2 H] fp32 (pi | pf)
-    const float* p0;            // wkv: w0 [H * Dk];  retention: decay [H];  mlstm: bias [2 H]
-    const float* p1;            // wkv: u [H * Dk]
+    const float* wpre; int wpre_stride; // wkv: d [rows, H * Dk] fp32;  mlstm: [rows, 2 H] fp32 (pi | pf);  delta: d [rows, H * Dk] or [rows, H]
+    const float* p0;            // wkv: w0 [H * Dk];  retention: decay [H];  mlstm: bias [2 H];  delta: A [H] (log of the rate)
+    const float* p1;            // wkv: u [H * Dk];  delta: b [H * Dk] or [H]
+    const float* bpre; int bpre_stride; // delta: the write strength's pre-activation [rows, H] fp32
+    int channel_decay;          // delta: a decay per key channel (else one per head)
+    int qk_group;               // value heads that share a head of q and k (1: every head has its own)
     const float* inv_freq; int rot_dims;    // retention: rotation of the first rot_dims values of q and k
     float k_scale, q_scale, cap;
     float* state; long long state_stride;  // [slots, state_stride]; a head's part starts at h * head_state
@@ -53,6 +62,9 @@ struct RecArgs {
 
 __device__ __forceinline__ float tw_logsigmoid(float x) {
     return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+}
+__device__ __forceinline__ float tw_softplus(float x) {
+    return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
 }
 
 template <typename T, int MODE>
@@ -77,7 +89,7 @@ linear_recurrence_kernel(RecArgs a) {
     const bool live = walks && j < cols;
     // a staged chunk: q [C][DK], k [C][DK], w [C][DK] (wkv) or gates [C][2] (mlstm), v [C][per]; two of them, so that
     // the rows of the next 16 tokens are staged while the state walks through these
-    const int extra = MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : 0);
+    const int extra = MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : (MODE == TW_REC_DELTA ? C * DK + 2 * C : 0));
     const int chunk_floats = 2 * C * DK + extra + C * per;
     float* su = sm + 2 * chunk_floats;      // [DK] bonus (wkv)
     const long long head_state = (long long)DK * cols + (MODE == TW_REC_MLSTM ? 1 : 0);
@@ -86,6 +98,7 @@ linear_recurrence_kernel(RecArgs a) {
     const T* __restrict__ gk = (const T*)a.k;
     const T* __restrict__ gv = (const T*)a.v;
     const int half = a.rot_dims >> 1;
+    const int hq = h / a.qk_group;      // the head of q and k this head reads
 
     // ---- the rows of up to C tokens from t0 on, as fp32: rotation, scaling, decays and gates are evaluated here
     auto stage = [&](int t0, float* buf, int tid, int nthreads) {
@@ -99,8 +112,8 @@ linear_recurrence_kernel(RecArgs a) {
             for (int e = tid; e < ct * half; e += nthreads) {
                 const int t = e / half, i = e - t * half;
                 const size_t row = (size_t)(start + t0 + t);
-                const T* qr = gq + row * a.q_stride + h * DK;
-                const T* kr = gk + row * a.k_stride + h * DK;
+                const T* qr = gq + row * a.q_stride + hq * DK;
+                const T* kr = gk + row * a.k_stride + hq * DK;
                 const float q1 = tw_to_float(qr[i]), q2 = tw_to_float(qr[i + half]);
                 const float k1 = tw_to_float(kr[i]), k2 = tw_to_float(kr[i + half]);
                 float sn, cs;
@@ -117,10 +130,20 @@ linear_recurrence_kernel(RecArgs a) {
         for (int e = tid; e < ct * plain; e += nthreads) {
             const int t = e / plain, i = first + (e - t * plain);
             const size_t row = (size_t)(start + t0 + t);
-            sq[t * DK + i] = tw_to_float(gq[row * a.q_stride + h * DK + i]) * a.q_scale;
-            sk[t * DK + i] = tw_to_float(gk[row * a.k_stride + h * DK + i]) * a.k_scale;
+            sq[t * DK + i] = tw_to_float(gq[row * a.q_stride + hq * DK + i]) * a.q_scale;
+            sk[t * DK + i] = tw_to_float(gk[row * a.k_stride + hq * DK + i]) * a.k_scale;
             if (MODE == TW_REC_WKV)
                 sw[t * DK + i] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
+            if (MODE == TW_REC_DELTA && a.channel_decay)
+                sw[t * DK + i] = expf(-expf(a.p0[h]) * tw_softplus(a.wpre[row * a.wpre_stride + h * DK + i] + a.p1[h * DK + i]));
+        }
+        if (MODE == TW_REC_DELTA) {
+            float* sg = sw + C * DK;        // [C] the head's decay (where it has one for all channels), [C] the write strength
+            for (int t = tid; t < ct; t += nthreads) {
+                const size_t row = (size_t)(start + t0 + t);
+                if (!a.channel_decay) sg[t] = expf(-expf(a.p0[h]) * tw_softplus(a.wpre[row * a.wpre_stride + h] + a.p1[h]));
+                sg[C + t] = 1.0f / (1.0f + expf(-a.bpre[row * a.bpre_stride + h]));
+            }
         }
         for (int e = tid; e < ct * per; e += nthreads) {     // the block's own columns of v
             const int t = e / per, c = blockIdx.z * per + (e - t * per);
@@ -179,6 +202,38 @@ linear_recurrence_kernel(RecArgs a) {
                 }
                 const float* w = sw + t * DK + ks * SK;
                 const float* u = su + ks * SK;
+                if constexpr (MODE == TW_REC_DELTA) {
+                    // one pass: decay the column, and form its products with k and with q, and k . q (four partial sums
+                    // each over the key channels i mod 4, the same order in every step)
+                    const float gh = a.channel_decay ? 1.f : sw[C * DK + t];
+                    const float beta = sw[C * DK + C + t];
+                    float r4[4] = {0.f, 0.f, 0.f, 0.f}, d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int i = 0; i < SK; ++i) {
+                        const float g = a.channel_decay ? w[i] : gh;
+                        S[i] *= g;
+                        r4[i & 3] += S[i] * k[i];
+                        acc4[i & 3] += S[i] * q[i];
+                        d4[i & 3] += k[i] * q[i];
+                    }
+                    float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+                    float p = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+                    float d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+                    if (KS > 1) {
+                        r += __shfl_xor_sync(0xffffffffu, r, 8);
+                        p += __shfl_xor_sync(0xffffffffu, p, 8);
+                        d += __shfl_xor_sync(0xffffffffu, d, 8);
+                        r += __shfl_xor_sync(0xffffffffu, r, 16);
+                        p += __shfl_xor_sync(0xffffffffu, p, 16);
+                        d += __shfl_xor_sync(0xffffffffu, d, 16);
+                    }
+                    const float uj = beta * (vj - r);
+#pragma unroll
+                    for (int i = 0; i < SK; ++i) S[i] += k[i] * uj;
+                    if (live && ks == 0)
+                        a.out[(size_t)(start + t0 + t) * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = p + uj * d;
+                    continue;
+                }
                 if constexpr (SK % 4 == 0) {
                     const float4* q4 = reinterpret_cast<const float4*>(q);
                     const float4* k4 = reinterpret_cast<const float4*>(k);
@@ -272,7 +327,8 @@ static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, c
     RecArgs b = a;
     b.cols_per_block = per;
     const size_t chunk = 2 * TW_REC_CHUNK * TW_DK + (size_t)TW_REC_CHUNK * per
-                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_DK : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : 0));
+                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_DK
+                            : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : (MODE == TW_REC_DELTA ? TW_REC_CHUNK * TW_DK + 2 * TW_REC_CHUNK : 0)));
     const size_t smem = (2 * chunk + TW_DK) * sizeof(float);
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(linear_recurrence_kernel<T, MODE>,
@@ -286,7 +342,8 @@ static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, c
 
 TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void* q, int q_stride, const void* k, int k_stride,
                                    const void* v, int v_stride, const float* wpre, int wpre_stride, const float* p0,
-                                   const float* p1, const float* inv_freq, int rot_dims, float q_scale, float k_scale,
+                                   const float* p1, const float* bpre, int bpre_stride, int channel_decay, int qk_group,
+                                   const float* inv_freq, int rot_dims, float q_scale, float k_scale,
                                    float cap, float* state, long long state_stride, const void* tail_src, int tail_stride,
                                    int tail_width, long long tail_offset, const int* positions, const int* seq_slot,
                                    const int* seq_q_start, const int* seq_q_len, int n_seqs, int H, int Dk, int Dv,
@@ -294,7 +351,9 @@ TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void*
     if (n_seqs <= 0 || H <= 0) return 0;
     const bool lp = max_q_len > TW_REC_CHUNK;
     if (Dk != TW_DK || Dv <= 0 || Dv > 256 || rot_dims < 0 || rot_dims > Dk || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
+    if (qk_group <= 0 || H % qk_group) return (int)cudaErrorInvalidValue;
     RecArgs a;
+    a.bpre = bpre; a.bpre_stride = bpre_stride; a.channel_decay = channel_decay; a.qk_group = qk_group;
     a.out = out; a.den = den; a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
     a.wpre = wpre; a.wpre_stride = wpre_stride; a.p0 = p0; a.p1 = p1; a.inv_freq = inv_freq; a.rot_dims = inv_freq ? rot_dims : 0;
     a.k_scale = k_scale; a.q_scale = q_scale; a.cap = cap; a.state = state; a.state_stride = state_stride;
@@ -313,6 +372,9 @@ TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void*
     case TW_REC_MLSTM:
         return f32 ? launch_recurrence<float, TW_REC_MLSTM>(a, n_seqs, lp, stream)
                    : launch_recurrence<__nv_bfloat16, TW_REC_MLSTM>(a, n_seqs, lp, stream);
+    case TW_REC_DELTA:
+        if (!f32 || !bpre || !wpre || !p0 || !p1) return (int)cudaErrorInvalidValue;     // its rows are prepared in fp32 in every run type
+        return launch_recurrence<float, TW_REC_DELTA>(a, n_seqs, lp, stream);
     }
     return (int)cudaErrorInvalidValue;
 }

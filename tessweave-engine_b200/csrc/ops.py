@@ -463,16 +463,17 @@ def rotate_heads(rows: torch.Tensor, bias: torch.Tensor | None, positions: torch
 
 
 def rotate_pairs(rows: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, inv_freq: torch.Tensor,
-                 n_tokens: int, n_heads: int, head_dim: int, rot_dims: int, interleaved: bool) -> None:
+                 n_tokens: int, n_heads: int, head_dim: int, rot_dims: int, interleaved: bool, magnitude: float = 1.0) -> None:
     """In place on the first ``n_heads`` heads of each packed row: rotate ``rot_dims / 2`` pairs at the start of
-    every head by ``position * inv_freq[i]``; pair i is (2i, 2i+1) when ``interleaved``, else (i, i + rot_dims / 2)."""
+    every head by ``position * inv_freq[i]``; pair i is (2i, 2i+1) when ``interleaved``, else (i, i + rot_dims / 2).
+    cos and sin are both multiplied by ``magnitude``."""
     _cuda(rows, positions, seq_of_token, inv_freq)
     _need(rows.stride(1) == 1 and rows.shape[1] >= n_heads * head_dim, "rotate_pairs: bad rows")
     _need(rot_dims % 2 == 0 and 0 <= rot_dims <= head_dim and inv_freq.dtype == torch.float32
           and inv_freq.numel() == rot_dims // 2, "rotate_pairs: inv_freq must be fp32 [rot_dims / 2], rot_dims even and <= D")
     code = _fn("elementwise", "tw_rotate_pairs")(_ptr(rows), c_int(rows.stride(0)), _ptr(positions), _ptr(seq_of_token),
                                                  _ptr(inv_freq), c_int(n_tokens), c_int(n_heads), c_int(head_dim),
-                                                 c_int(rot_dims), c_int(1 if interleaved else 0),
+                                                 c_int(rot_dims), c_int(1 if interleaved else 0), c_float(magnitude),
                                                  c_int(dtype_code(rows.dtype)), _stream())
     _check(code, "rotate_pairs")
 
@@ -505,11 +506,19 @@ def silu_mul(out: torch.Tensor, gate_up, n_rows: int, interleaved: bool = False)
 def attention_generic(out: torch.Tensor, q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                       seq_slot: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       n_tokens: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
-                      status: torch.Tensor) -> None:
+                      status: torch.Tensor, sink: torch.Tensor | None = None,
+                      bias_by_distance: torch.Tensor | None = None) -> None:
     """Exact paged causal attention, one block per (token, head).  q may be a column
     slice of the packed qkv buffer (row stride is passed on).  The value pages may have rows of another
-    length than the key pages; the output then has heads of that length."""
-    _cuda(out, q, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status)
+    length than the key pages (or be the key pages themselves); the output then has heads of that length.
+    ``sink`` fp32 [Hq]: exp(sink[h]) joins the softmax's denominator.  ``bias_by_distance`` fp32 [rows, Hq]: row
+    min(position - key position, rows - 1) is added to the scaled score."""
+    _cuda(out, q, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status, sink, bias_by_distance)
+    _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == n_q_heads and sink.is_contiguous()),
+          "attention: the sink must be fp32 [Hq]")
+    _need(bias_by_distance is None or (bias_by_distance.dtype == torch.float32 and bias_by_distance.dim() == 2
+                                       and bias_by_distance.shape[1] == n_q_heads and bias_by_distance.is_contiguous()
+                                       and bias_by_distance.shape[0] > 0), "attention: the distance bias must be fp32 [rows, Hq]")
     _need(head_dim <= 256 and v_pages.shape[3] <= 256, f"attention: head sizes above 256 are not supported")
     _need(k_pages.shape[3] == head_dim and k_pages.shape[:3] == v_pages.shape[:3] and k_pages.is_contiguous()
           and v_pages.is_contiguous(), "attention: pages must be contiguous [pages, kv_heads, page, head size]")
@@ -520,7 +529,9 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, positions: torch.Tenso
         _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(positions), _ptr(seq_of_token),
         _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_tokens),
         c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_pages.shape[3]), c_int(k_pages.shape[2]),
-        c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+        c_int(k_pages.shape[0]), c_int(window), c_float(scale), _ptr(bias_by_distance),
+        c_int(0 if bias_by_distance is None else bias_by_distance.shape[0]), _ptr(sink), c_int(dtype_code(q.dtype)),
+        _ptr(status), _stream())
     _check(code, "attention_generic")
 
 
@@ -1200,7 +1211,7 @@ def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: 
 # ---------------------------------------------------------------------------
 # pieces of mixers that are not attention over a cache: recurrences with a matrix state, token shift
 # ---------------------------------------------------------------------------
-RECURRENCE_RETENTION, RECURRENCE_WKV, RECURRENCE_MLSTM = 0, 1, 2
+RECURRENCE_RETENTION, RECURRENCE_WKV, RECURRENCE_MLSTM, RECURRENCE_DELTA = 0, 1, 2, 3
 RECURRENCE_MAX_KEY_DIM = 256      # a thread keeps a column of the state in registers (beyond 128 it spills)
 
 
@@ -1217,15 +1228,27 @@ def linear_recurrence(mode: int, out: torch.Tensor, den: torch.Tensor | None, q:
                       seq_q_len: torch.Tensor, n_seqs: int, heads: int, key_dim: int, value_dim: int, write_state: bool = True,
                       pre: torch.Tensor | None = None, p0: torch.Tensor | None = None, p1: torch.Tensor | None = None,
                       inv_freq: torch.Tensor | None = None, rot_dims: int = 0, q_scale: float = 1.0, k_scale: float = 1.0,
-                      cap: float = 1.0, tail: torch.Tensor | None = None, tail_offset: int = 0, max_q_len: int = 1 << 30) -> None:
+                      cap: float = 1.0, tail: torch.Tensor | None = None, tail_offset: int = 0, max_q_len: int = 1 << 30,
+                      write_pre: torch.Tensor | None = None, channel_decay: bool = False, qk_group: int = 1) -> None:
     """Walk every request's rows of the step through its matrix state (csrc/linear_recurrence.cu): ``out`` fp32
     [rows, heads * value_dim] receives the raw outputs, ``den`` fp32 [rows, heads] the mLSTM denominators.  q, k, v are
     column slices of the projected rows (heads side by side).  ``pre``: fp32 rows the rule needs beside them (wkv:
     the projected decay [rows, heads * key_dim]; mlstm: the gates' pre-activations [rows, 2 * heads]); ``p0`` / ``p1``
     fp32 constants (wkv: decay offset and bonus; retention: decay per head; mlstm: gate biases).  ``tail``: rows whose
     last one per request is copied into the state behind the heads (wkv's token shift), at ``tail_offset``.
-    ``max_q_len``: the longest portion of the step (a hint: steps of single tokens launch smaller blocks)."""
-    _cuda(out, den, q, k, v, state, positions, seq_slot, seq_q_start, seq_q_len, pre, p0, p1, inv_freq, tail)
+    ``max_q_len``: the longest portion of the step (a hint: steps of single tokens launch smaller blocks).
+    The delta rule takes fp32 q, k, v that are ready to use, ``pre`` the projected decay ([rows, heads * key_dim] with
+    ``channel_decay``, else [rows, heads]), ``p0`` the log of each head's rate [heads], ``p1`` the decay's bias (of
+    ``pre``'s width), ``write_pre`` the write strength before its sigmoid, fp32 [rows, heads]; ``qk_group`` value heads
+    share a head of q and k."""
+    _cuda(out, den, q, k, v, state, positions, seq_slot, seq_q_start, seq_q_len, pre, p0, p1, inv_freq, tail, write_pre)
+    if mode == RECURRENCE_DELTA:
+        width = heads * key_dim if channel_decay else heads
+        _need(q.dtype == torch.float32 and pre is not None and p0 is not None and p1 is not None and write_pre is not None
+              and write_pre.dtype == torch.float32 and write_pre.stride(1) == 1 and write_pre.shape[1] >= heads
+              and pre.stride(1) == 1 and pre.shape[1] >= width and p1.numel() == width and p0.numel() == heads
+              and qk_group >= 1 and heads % qk_group == 0,
+              "recurrence: the delta rule needs fp32 rows, a projected decay with its rate and bias, and a write strength")
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == heads * value_dim, "recurrence: out must be fp32 [rows, H * Dv]")
     _need(q.dtype == k.dtype == v.dtype and q.stride(1) == k.stride(1) == v.stride(1) == 1, "recurrence: q, k, v of one type, unit column stride")
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1, "recurrence: state must be fp32 [slots, numel]")
@@ -1237,7 +1260,9 @@ def linear_recurrence(mode: int, out: torch.Tensor, den: torch.Tensor | None, q:
     _need(mode != RECURRENCE_RETENTION or p0 is not None, "recurrence: retention needs a decay per head")
     code = _fn("linear_recurrence", "tw_linear_recurrence", {"TW_DK": key_dim})(
         c_int(mode), _ptr(out), _ptr(den), _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), _ptr(v), c_int(v.stride(0)),
-        _ptr(pre), c_int(0 if pre is None else pre.stride(0)), _ptr(p0), _ptr(p1), _ptr(inv_freq), c_int(rot_dims),
+        _ptr(pre), c_int(0 if pre is None else pre.stride(0)), _ptr(p0), _ptr(p1), _ptr(write_pre),
+        c_int(0 if write_pre is None else write_pre.stride(0)), c_int(1 if channel_decay else 0), c_int(qk_group),
+        _ptr(inv_freq), c_int(rot_dims),
         c_float(q_scale), c_float(k_scale), c_float(cap), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(tail),
         c_int(0 if tail is None else tail.stride(0)), c_int(0 if tail is None else tail.shape[1]), ctypes.c_longlong(tail_offset),
         _ptr(positions), _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(heads), c_int(key_dim),
@@ -1340,17 +1365,20 @@ def add_bias_rows(rows: torch.Tensor, bias: torch.Tensor, n_rows: int) -> None:
 
 
 def kv_store(rows: torch.Tensor, k_col: int, v_col: int, positions: torch.Tensor, seq_of_token: torch.Tensor, seq_slot: torch.Tensor,
-             block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, n_tokens: int, status: torch.Tensor) -> None:
+             block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor | None, n_tokens: int,
+             status: torch.Tensor) -> None:
     """Copy the keys (columns from ``k_col``) and values (from ``v_col``) of the step's packed rows into their pages;
-    key pages are [pages, kv_heads, page, Dk], value pages [pages, kv_heads, page, Dv]."""
+    key pages are [pages, kv_heads, page, Dk], value pages [pages, kv_heads, page, Dv].  ``v_pages`` None: only the keys
+    are stored (a mixer whose values are its keys keeps one set of pages)."""
     _cuda(rows, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status)
-    _need(rows.stride(1) == 1 and rows.dtype == k_pages.dtype == v_pages.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
-          and k_pages.shape[:3] == v_pages.shape[:3], "kv_store: pages must be contiguous and of the rows' type")
+    _need(rows.stride(1) == 1 and rows.dtype == k_pages.dtype and k_pages.is_contiguous(), "kv_store: pages must be contiguous and of the rows' type")
+    _need(v_pages is None or (v_pages.dtype == rows.dtype and v_pages.is_contiguous() and k_pages.shape[:3] == v_pages.shape[:3]),
+          "kv_store: value pages must be contiguous, of the rows' type and as many as the key pages")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "kv_store: bad block table")
     code = _fn("elementwise", "tw_kv_store")(
         _ptr(rows), c_int(rows.stride(0)), c_int(k_col), c_int(v_col), _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_tokens), c_int(k_pages.shape[1]),
-        c_int(k_pages.shape[3]), c_int(v_pages.shape[3]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
+        c_int(k_pages.shape[3]), c_int(0 if v_pages is None else v_pages.shape[3]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
         c_int(dtype_code(rows.dtype)), _ptr(status), _stream())
     _check(code, "kv_store")
 
@@ -1451,3 +1479,87 @@ def moe_combine(out: torch.Tensor, ys: torch.Tensor, place: torch.Tensor, weight
     code = _fn("moe", "tw_moe_combine")(_ptr(out), _ptr(ys), _ptr(place), _ptr(weight), _ptr(shared), _ptr(shared_gate),
                                         c_int(n_rows), c_int(top), c_int(width), c_int(dtype_code(out.dtype)), _stream())
     _check(code, "moe_combine")
+
+
+def add_row_vector(resid: torch.Tensor, vec: torch.Tensor, n_rows: int) -> None:
+    """resid[:n_rows] += vec: a learned fp32 vector added to every row of the fp32 residual stream."""
+    _cuda(resid, vec)
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and vec.dtype == torch.float32 and vec.is_contiguous()
+          and vec.numel() == resid.shape[1] and resid.shape[0] >= n_rows, "add_row_vector: fp32 [rows, width] and fp32 [width]")
+    code = _fn("elementwise", "tw_add_row_vector")(_ptr(resid), _ptr(vec), c_int(n_rows), c_int(resid.shape[1]), _stream())
+    _check(code, "add_row_vector")
+
+
+def add_delta(resid: torch.Tensor, delta, n_rows: int) -> None:
+    """resid[:n_rows] += delta in fp32; ``delta`` is a tensor [rows, width] (bfloat16 or fp32) or a ``SplitSum``."""
+    width = resid.shape[1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape[0] >= n_rows, "add_delta: the residual stream must be contiguous fp32")
+    if isinstance(delta, SplitSum):
+        slices = delta.slices
+        _cuda(resid, slices)
+        _need(slices.dtype == torch.float32 and slices.shape[2] == width and slices[0].is_contiguous() and slices.shape[1] >= n_rows,
+              "add_delta: split sum must be fp32 [slices, rows, width]")
+        code = _fn("elementwise", "tw_add_delta")(_ptr(resid), _ptr(None), _ptr(slices), c_int(slices.shape[0]),
+                                                  ctypes.c_longlong(slices.stride(0)), ctypes.c_longlong(n_rows * width), c_int(F32), _stream())
+    else:
+        _cuda(resid, delta)
+        _need(delta.is_contiguous() and delta.shape[1] == width and delta.shape[0] >= n_rows, "add_delta: delta must be contiguous [rows, width]")
+        code = _fn("elementwise", "tw_add_delta")(_ptr(resid), _ptr(delta), _ptr(None), c_int(0), ctypes.c_longlong(0),
+                                                  ctypes.c_longlong(n_rows * width), c_int(dtype_code(delta.dtype)), _stream())
+    _check(code, "add_delta")
+
+
+def normed_accumulate(acc: torch.Tensor, out: torch.Tensor | None, x: torch.Tensor, weight: torch.Tensor, eps: float, scale: float,
+                      first: bool, n_rows: int) -> None:
+    """acc[r] = (0 if first else acc[r]) + scale * x[r] / sqrt(mean(x[r]^2) + eps) * weight, row by row in fp32; ``out``
+    (may be None) receives the new sum in x's type."""
+    _cuda(acc, out, x, weight)
+    width = x.shape[1]
+    _need(acc.dtype == torch.float32 and acc.is_contiguous() and x.is_contiguous() and acc.shape[1] == width
+          and min(acc.shape[0], x.shape[0]) >= n_rows and weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == width
+          and (out is None or (out.dtype == x.dtype and out.is_contiguous() and out.shape[1] == width and out.shape[0] >= n_rows)),
+          "normed_accumulate: fp32 sum, rows of one type and shape, an fp32 weight of their width")
+    code = _fn("elementwise", "tw_normed_accumulate")(_ptr(acc), _ptr(out), _ptr(x), _ptr(weight), c_float(eps), c_float(scale),
+                                                      c_int(1 if first else 0), c_int(n_rows), c_int(width), c_int(dtype_code(x.dtype)), _stream())
+    _check(code, "normed_accumulate")
+
+
+SHORT_CONV_MAX_TAPS = 17
+
+
+def short_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, state_offset: int,
+               seq_of_token: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor, n_rows: int,
+               unit_heads: int = 0, unit_dim: int = 0, scaled_heads: int = 0, head_scale: float = 1.0, unit_eps: float = 0.0) -> None:
+    """out[t, c] = silu(sum_j w[c, j] x[t - (taps - 1) + j, c]) in fp32 [rows, channels]: a causal convolution over the
+    rows of each request, per channel (the last tap is the row's own).  The taps - 1 rows before a request's first row of
+    this step are read from its state (fp32, [channels, taps - 1] at ``state_offset``; zeros at a request's start).  The
+    first ``unit_heads`` heads of ``unit_dim`` channels are then scaled to x / sqrt(sum x^2 + unit_eps), the first
+    ``scaled_heads`` of those also by ``head_scale``.  ``short_conv_state`` moves the state on afterwards."""
+    _cuda(out, x, w, state, seq_of_token, seq_slot, seq_q_start)
+    channels, taps = w.shape
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == channels and out.shape[0] >= n_rows,
+          "short_conv: the result must be contiguous fp32 [rows, channels]")
+    _need(x.stride(1) == 1 and x.shape[1] >= channels and x.shape[0] >= n_rows, "short_conv: bad input rows")
+    _need(w.dtype == torch.float32 and w.is_contiguous() and 1 <= taps <= SHORT_CONV_MAX_TAPS, "short_conv: taps must be fp32 [channels, 1..17]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state_offset + channels * (taps - 1) <= state.shape[1], "short_conv: the state must be fp32 [slots, numel] with room for the taps")
+    _need(0 <= scaled_heads <= unit_heads and unit_heads * unit_dim <= channels, "short_conv: the unit heads exceed the channels")
+    code = _fn("recurrent", "tw_short_conv")(
+        _ptr(out), _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(taps), _ptr(state), ctypes.c_longlong(state.stride(0)),
+        ctypes.c_longlong(state_offset), _ptr(seq_of_token), _ptr(seq_slot), _ptr(seq_q_start), c_int(n_rows), c_int(channels),
+        c_int(unit_heads), c_int(unit_dim), c_int(scaled_heads), c_float(head_scale), c_float(unit_eps), c_int(dtype_code(x.dtype)), _stream())
+    _check(code, "short_conv")
+
+
+def short_conv_state(x: torch.Tensor, taps: int, channels: int, state: torch.Tensor, state_offset: int, seq_slot: torch.Tensor,
+                     seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int) -> None:
+    """After ``short_conv``: every request's state keeps the last ``taps - 1`` inputs (older ones stay where the step
+    brought fewer rows than that)."""
+    _cuda(x, state, seq_slot, seq_q_start, seq_q_len)
+    _need(x.stride(1) == 1 and x.shape[1] >= channels and 1 <= taps <= SHORT_CONV_MAX_TAPS, "short_conv_state: bad input rows or taps")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state_offset + channels * (taps - 1) <= state.shape[1], "short_conv_state: the state must be fp32 [slots, numel] with room for the taps")
+    code = _fn("recurrent", "tw_short_conv_state")(
+        _ptr(x), c_int(x.stride(0)), c_int(taps), _ptr(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(state_offset),
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(channels), c_int(dtype_code(x.dtype)), _stream())
+    _check(code, "short_conv_state")

@@ -329,3 +329,109 @@ TW_EXPORT int tw_tanh_rows(void* x, long long count, int dtype, cudaStream_t str
     if (dtype == TW_F32) return tw_launch(tanh_rows_kernel<float>, grid, dim3(256), 0, stream, 1, (float*)x, (size_t)count);
     return tw_launch(tanh_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, (__nv_bfloat16*)x, (size_t)count);
 }
+
+// ---------------------------------------------------------------------------
+// Short causal convolution over time, per channel, with silu, for the packed rows a recurrence reads:
+//   y[t, c] = silu(sum_j w[c, j] x[t - (taps - 1) + j, c]),   the last tap is the row's own, zeros before a request's start.
+// The taps - 1 rows before a request's first row of this step come from the request's state (fp32, channel-major:
+// state[offset + c * (taps - 1) + j], j = 0 the oldest), which tw_short_conv_state moves on afterwards.  Behind the
+// convolution the first `unit_heads` heads of `unit_dim` channels are scaled to unit length, x / sqrt(sum x^2 + unit_eps),
+// the first `scaled_heads` of them also multiplied by `head_scale`.  One block per row; the result is fp32.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+short_conv_kernel(float* __restrict__ out, const T* __restrict__ x, int x_stride, const float* __restrict__ w, int taps,
+                  const float* __restrict__ state, long long state_stride, long long state_offset,
+                  const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
+                  int channels, int unit_heads, int unit_dim, int scaled_heads, float head_scale, float unit_eps) {
+    extern __shared__ float sy[];        // [channels]
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int row = blockIdx.x;
+    const int s = seq_of_token[row];
+    if (s < 0) return;
+    const int r = row - seq_q_start[s];                  // rows of this request before this one in the step
+    const float* tail = state + (size_t)seq_slot[s] * state_stride + state_offset;
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j;               // how many rows before this one
+            const float xv = back <= r ? tw_to_float(x[(size_t)(row - back) * x_stride + c])
+                                       : tail[(size_t)c * (taps - 1) + (taps - 1 + r - back)];
+            acc += w[(size_t)c * taps + j] * xv;
+        }
+        sy[c] = acc / (1.0f + expf(-acc));
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    float* orow = out + (size_t)row * channels;
+    for (int head = warp; head < unit_heads; head += nwarps) {
+        const float* y = sy + head * unit_dim;
+        float ss = 0.f;
+        for (int d = lane; d < unit_dim; d += 32) ss += y[d] * y[d];
+        ss = tw_warp_sum(ss);
+        const float f = (head < scaled_heads ? head_scale : 1.0f) / sqrtf(ss + unit_eps);
+        for (int d = lane; d < unit_dim; d += 32) orow[head * unit_dim + d] = y[d] * f;
+    }
+    for (int c = unit_heads * unit_dim + threadIdx.x; c < channels; c += blockDim.x) orow[c] = sy[c];
+}
+
+// The convolution's state after the step: the last taps - 1 inputs of every request, older ones kept where the
+// step brought fewer rows than that.  One thread per (request, channel) reads its old values before it writes.
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ x, int x_stride, int taps, float* __restrict__ state,
+                                        long long state_stride, long long state_offset, const int* __restrict__ seq_slot,
+                                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len, int channels) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int len = seq_q_len[s];
+    if (c >= channels || len <= 0) return;
+    const int start = seq_q_start[s], keep = taps - 1;
+    float* tail = state + (size_t)seq_slot[s] * state_stride + state_offset + (size_t)c * keep;
+    float fresh[16];
+    for (int j = 0; j < keep; ++j) {
+        const int r = len - keep + j;                    // the step's row that lands at place j (negative: an older one)
+        fresh[j] = r >= 0 ? tw_to_float(x[(size_t)(start + r) * x_stride + c]) : tail[j + len];
+    }
+    for (int j = 0; j < keep; ++j) tail[j] = fresh[j];
+}
+
+TW_EXPORT int tw_short_conv(float* out, const void* x, int x_stride, const float* w, int taps, float* state,
+                            long long state_stride, long long state_offset, const int* seq_of_token, const int* seq_slot,
+                            const int* seq_q_start, int n_rows, int channels, int unit_heads, int unit_dim, int scaled_heads,
+                            float head_scale, float unit_eps, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0 || channels <= 0) return 0;
+    if (taps < 1 || taps > 17 || unit_heads * unit_dim > channels) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)channels * sizeof(float);
+    if (dtype == TW_F32) {
+        if (smem > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(short_conv_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return tw_launch(short_conv_kernel<float>, dim3(n_rows), dim3(256), smem, stream, 1, out, (const float*)x, x_stride, w, taps,
+                         (const float*)state, state_stride, state_offset, seq_of_token, seq_slot, seq_q_start, channels,
+                         unit_heads, unit_dim, scaled_heads, head_scale, unit_eps);
+    }
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(short_conv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return tw_launch(short_conv_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), smem, stream, 1, out, (const __nv_bfloat16*)x,
+                     x_stride, w, taps, (const float*)state, state_stride, state_offset, seq_of_token, seq_slot, seq_q_start,
+                     channels, unit_heads, unit_dim, scaled_heads, head_scale, unit_eps);
+}
+
+TW_EXPORT int tw_short_conv_state(const void* x, int x_stride, int taps, float* state, long long state_stride,
+                                  long long state_offset, const int* seq_slot, const int* seq_q_start, const int* seq_q_len,
+                                  int n_seqs, int channels, int dtype, cudaStream_t stream) {
+    if (n_seqs <= 0 || channels <= 0 || taps <= 1) return 0;
+    if (taps > 17) return (int)cudaErrorInvalidValue;
+    const dim3 grid((channels + 127) / 128, n_seqs);
+    if (dtype == TW_F32)
+        return tw_launch(short_conv_state_kernel<float>, grid, dim3(128), 0, stream, 1, (const float*)x, x_stride, taps, state,
+                         state_stride, state_offset, seq_slot, seq_q_start, seq_q_len, channels);
+    return tw_launch(short_conv_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, (const __nv_bfloat16*)x, x_stride, taps,
+                     state, state_stride, state_offset, seq_slot, seq_q_start, seq_q_len, channels);
+}

@@ -4,5 +4,6 @@ from .model import Model
 from . import qwen2  # noqa: F401  (registers "Qwen2ForCausalLM")
 from . import linurax  # noqa: F401  (registers "Linurax")
 from . import sapatar  # noqa: F401  (registers "Sapatar")
+from . import nufatar  # noqa: F401  (registers "Nufatar")
 
 __all__ = ["LayerSpec", "ModelSpec", "ScheduleEntry", "Model"]

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
 from ..parts.base import FixedState, PagedKV, Runtime, StepContext, WeightDecl, build_part, flat_needs, join_name
 from .spec import ModelSpec
 
@@ -24,6 +25,9 @@ class Model:
             raise ValueError(f"embedding kind {spec.embedding.kind!r} has no matrix a head could be tied to")
         self.head = build_part("head", spec.head, runtime, **({"tied": tied} if tied is not None else {}))
         self.graph_safe = all(p.graph_safe for p in (self.embedding, *self.blocks, self.final_norm, self.head))
+        # learned vectors that runs of the schedule add to the stream (one per pass of a repeated range of layers)
+        self.pass_vectors = (runtime.empty(spec.pass_vectors[1], spec.hidden_size, dtype=torch.float32)
+                             if spec.pass_vectors is not None else None)
         self.loaded = False
         self.tap = None      # callable(schedule entry, stream) run behind every block: for looking at a step layer by layer
 
@@ -46,6 +50,11 @@ class Model:
                 if name in decls:
                     raise ValueError(f"two parts declare the weight {name!r}")
                 decls[name] = WeightDecl(name, tuple(w.shape), w.role, w.init, w.dest)
+        if self.pass_vectors is not None:
+            name = self.spec.pass_vectors[0]
+            if name in decls:
+                raise ValueError(f"two parts declare the weight {name!r}")
+            decls[name] = WeightDecl(name, tuple(self.pass_vectors.shape), "vector", "normal", self.pass_vectors)
         return decls
 
     def redundant_names(self) -> set[str]:
@@ -90,7 +99,7 @@ class Model:
     def cache_bytes_per_token(self, element_bytes: int) -> int:
         """Bytes of keys and values one token adds to the paged groups (all layers; a windowed layer
         counts like any other: the window bounds how many tokens are held, not their size)."""
-        return sum(need.kv_heads * (need.head_dim + need.value_dim) * element_bytes
+        return sum(need.kv_heads * (need.head_dim + (0 if need.values_are_keys else need.value_dim)) * element_bytes
                    for entry, _ in self.cache_needs() for need in flat_needs(entry) if isinstance(need, PagedKV))
 
     def state_bytes_per_request(self) -> int:
@@ -111,6 +120,11 @@ class Model:
             raise RuntimeError("the model has no weights yet: load them or write random ones first")
         stream = self.embedding.forward(ctx)
         for i, entry in enumerate(self.spec.schedule):
+            if entry.add_vector is not None:
+                if stream.copies is not None:
+                    raise RuntimeError("a pass vector cannot be added to a stream that is kept as several copies")
+                ops.add_row_vector(stream.resid, self.pass_vectors[entry.add_vector], ctx.n_tokens)
+                stream.rounded = None
             self.blocks[entry.layer].forward(ctx, stream, caches[i], write_cache=entry.cache_of is None)
             if self.tap is not None:
                 self.tap(i, ctx, stream)

@@ -16,9 +16,11 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``cache_of`` names an earlier schedule entry whose cache this run
-    reads instead of writing one of its own; ``None`` gives the run its own cache."""
+    reads instead of writing one of its own; ``None`` gives the run its own cache.  ``add_vector`` names a row of
+    the model's pass vectors (``ModelSpec.pass_vectors``) that is added to the residual stream ahead of this run."""
     layer: int
     cache_of: int | None = None
+    add_vector: int | None = None
 
 
 @dataclass(frozen=True)
@@ -39,11 +41,14 @@ class ModelSpec:
     eos_token_ids: tuple[int, ...] = ()
     init_std: float = 0.02
     ignored_suffixes: tuple[str, ...] = ()    # checkpoint tensors that are derived, not weights
+    pass_vectors: tuple[str, int] | None = None   # (tensor name, rows): learned [rows, hidden] vectors that schedule entries add to the stream
 
     def __post_init__(self):
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, but there are {len(self.layers)} layers")
+            if e.add_vector is not None and (self.pass_vectors is None or not 0 <= e.add_vector < self.pass_vectors[1]):
+                raise ValueError(f"schedule entry {i} adds pass vector {e.add_vector}, which the model does not have")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i:
                     raise ValueError(f"schedule entry {i} may only read the cache of an earlier entry")

@@ -1,6 +1,8 @@
 """Grouped-query attention over a paged cache."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..csrc import ops
@@ -27,6 +29,14 @@ class GQAAttention(Mixer):
     head); the output then has ``n_heads`` heads of that size.  Such a mixer, and one whose position encoding no
     kernel applies on the way, adds the bias, applies the encoding and stores keys and values as separate
     steps, and attends with the exact kernel; everything else takes the fused and tensor-core kernels.
+
+    ``values_are_keys``: there is no value projection; a position's value is its key as projected (and encoded), and
+    the cache keeps one set of pages for both.  ``sink`` (a tensor name): a learned number per query head whose
+    exponential joins the softmax's denominator -- it has no key and no value, is not scaled and counts once.
+    ``distance_bias`` (``name``, ``rows``, ``far``): a learned table [rows, n_heads] added to the scaled score by
+    bucketed distance n = position - key position: bucket(n) = n below rows // 2, else
+    min(rows - 1, rows // 2 + floor(ln(n / (rows // 2)) / ln(far / (rows // 2)) * (rows - rows // 2))); the table by
+    plain distance is made once, when the weights are in.  A mixer with any of the three attends with the exact kernel.
     """
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
@@ -34,7 +44,8 @@ class GQAAttention(Mixer):
 
     def __init__(self, runtime: Runtime, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, scale: float | None = None, window: int | None = None,
-                 out_bias: bool = False, v_head_dim: int | None = None, names: dict[str, str] | None = None):
+                 out_bias: bool = False, v_head_dim: int | None = None, names: dict[str, str] | None = None,
+                 values_are_keys: bool = False, sink: str | None = None, distance_bias: dict | None = None):
         super().__init__(runtime)
         if min(hidden, n_heads, n_kv_heads, head_dim) <= 0 or n_heads % n_kv_heads:
             raise ValueError("attention: heads must be positive and n_heads a multiple of n_kv_heads")
@@ -49,32 +60,72 @@ class GQAAttention(Mixer):
         if not 0 < self.v_dim <= 256:
             raise ValueError(f"attention: v_head_dim {self.v_dim} must lie in 1..256")
         self.same_dims = self.v_dim == head_dim
+        self.values_are_keys = bool(values_are_keys)
+        if self.values_are_keys and (not self.same_dims or qkv_bias):
+            raise ValueError("attention: values that are the keys have the keys' size and no bias of their own")
         self.names = {**self.NAMES, **(names or {})}
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.window = window
         self.q_size, self.kv_size = n_heads * head_dim, n_kv_heads * head_dim
-        self.v_size, self.out_size = n_kv_heads * self.v_dim, n_heads * self.v_dim
+        self.v_size, self.out_size = (0 if self.values_are_keys else n_kv_heads * self.v_dim), n_heads * self.v_dim
         self.qkv_width = self.q_size + self.kv_size + self.v_size
         self.position = build_part("position", position, runtime)
         self.w_qkv = runtime.empty(self.qkv_width, hidden)
         self.b_qkv = runtime.empty(self.qkv_width, dtype=torch.float32) if qkv_bias else None
         self.w_o = runtime.empty(hidden, self.out_size)
+        self.sink_name = sink
+        self.sink = runtime.empty(n_heads, dtype=torch.float32) if sink is not None else None
+        self.distance_bias = None
+        self.bias_by_distance = None
+        if distance_bias is not None:
+            rows, far = int(distance_bias["rows"]), float(distance_bias["far"])
+            if rows < 2 or not far > rows // 2:
+                raise ValueError(f"attention: a distance table needs at least 2 rows and a far distance beyond rows // 2, got {rows} and {far}")
+            self.distance_bias = {"name": str(distance_bias["name"]), "rows": rows, "far": far}
+            self.bias_table = runtime.empty(rows, n_heads, dtype=torch.float32)
+        # what only the exact kernel knows
+        self.exact_only = self.values_are_keys or self.sink is not None or self.distance_bias is not None
+
+    @staticmethod
+    def distance_bucket(n: int, rows: int, far: float) -> int:
+        half = rows // 2
+        if n < half:
+            return n
+        return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+    def finalize(self) -> None:
+        if self.distance_bias is not None:
+            # every distance a query can see, row by row; distances from the last row on share its bucket (the last)
+            rows, far = self.distance_bias["rows"], self.distance_bias["far"]
+            reach = int(math.ceil(far)) + 1
+            if self.window is not None:
+                reach = min(reach, self.window)
+            buckets = [self.distance_bucket(n, rows, far) for n in range(reach)]
+            index = torch.tensor(buckets, dtype=torch.long, device=self.bias_table.device)
+            self.bias_by_distance = self.bias_table.index_select(0, index).contiguous()
 
     def weights(self) -> list[WeightDecl]:
         q, kv, nm = self.q_size, self.kv_size, self.names
-        spans = (("q", 0, q), ("k", q, q + kv), ("v", q + kv, self.qkv_width))
+        spans = (("q", 0, q), ("k", q, q + kv)) + ((("v", q + kv, self.qkv_width),) if not self.values_are_keys else ())
+        extra = []
+        if self.sink is not None:
+            extra.append(WeightDecl(self.sink_name, (self.n_heads,), role="vector", dest=self.sink))
+        if self.distance_bias is not None:
+            extra.append(WeightDecl(self.distance_bias["name"], (self.distance_bias["rows"], self.n_heads), role="vector",
+                                    dest=self.bias_table))
         decls = [WeightDecl(nm[n], (e - b, self.hidden), dest=self.w_qkv[b:e]) for n, b, e in spans]
         if self.b_qkv is not None:
             decls += [WeightDecl(nm[f"{n}_bias"], (e - b,), role="vector", dest=self.b_qkv[b:e]) for n, b, e in spans]
         decls.append(WeightDecl(nm["o"], (self.hidden, self.out_size), dest=self.w_o))
-        return decls
+        return decls + extra
 
     def cache_need(self) -> PagedKV:
-        return PagedKV(self.n_kv_heads, self.head_dim, self.window, None if self.same_dims else self.v_dim)
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window, None if self.same_dims else self.v_dim,
+                       values_are_keys=self.values_are_keys)
 
     def _fused_table(self):
         """The rotation table of the kernels that rotate on the way; None where the mixer takes the separate steps."""
-        return self.position.fused_rotary_table(self.head_dim) if self.same_dims else None
+        return self.position.fused_rotary_table(self.head_dim) if self.same_dims and not self.exact_only else None
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
         if not isinstance(cache, PagedView):
@@ -145,14 +196,15 @@ class GQAAttention(Mixer):
             # decode-only step: the attention kernel adds the bias, rotates, writes the new key and value and attends
             self._decode(ctx, out, None, cache, fused=(source if source is not None else qkv, table, write_cache))
             return out
-        if not self.same_dims:
-            # keys and values of different sizes: bias, the position part's own transformation, then the store
+        if not self.same_dims or self.exact_only:
+            # keys and values of different sizes, or what only the exact kernel knows: bias, the position part's own
+            # transformation, then the store (values that are the keys share the keys' pages: one store)
             if self.b_qkv is not None:
                 ops.add_bias_rows(qkv, self.b_qkv, n)
             self.position.apply(ctx, qkv, self.n_heads + self.n_kv_heads, self.head_dim)
             if write_cache:
                 ops.kv_store(qkv, self.q_size, self.q_size + self.kv_size, ctx.positions, ctx.seq_of_token, ctx.seq_slot,
-                             cache.block_table, cache.k_pages, cache.v_pages, n, ctx.status)
+                             cache.block_table, cache.k_pages, None if self.values_are_keys else cache.v_pages, n, ctx.status)
             self._attend(ctx, out, qkv, cache)
             return out
         if table is None:
@@ -220,9 +272,10 @@ class GQAAttention(Mixer):
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
         q = qkv[:, : self.q_size]
-        if self.same_dims and ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim):
+        if self.same_dims and not self.exact_only and ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim):
             self._attend_tensor_cores(ctx, out, q, cache)
             return
         ops.attention_generic(out, q, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table,
                               cache.k_pages, cache.v_pages, ctx.n_tokens, self.n_heads, self.n_kv_heads,
-                              self.head_dim, self.window or 0, self.scale, ctx.status)
+                              self.head_dim, self.window or 0, self.scale, ctx.status, sink=self.sink,
+                              bias_by_distance=self.bias_by_distance)

@@ -56,7 +56,7 @@ class WeightDecl:
     in 32 bits stays so; bf16 widens exactly), ``table_int`` in int32.  ``dest`` is
     the device storage the loader copies into, usually a slice of a packed buffer.
     ``init`` is the random-weights rule: ``normal`` ~ N(0, std), ``one_plus_normal``
-    ~ 1 + N(0, 0.1), ``eye_plus_normal`` ~ I + N(0, std), ``zeros``.
+    ~ 1 + N(0, 0.1), ``eye_plus_normal`` ~ I + N(0, std), ``wide_normal`` ~ N(0, 0.4), ``zeros``.
     """
     name: str
     shape: tuple[int, ...]
@@ -71,11 +71,13 @@ class WeightDecl:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values for every token (or the last ``window`` tokens), in pages.  ``v_head_dim``: the size of
-    a value row where it differs from a key row's (``None``: the same)."""
+    a value row where it differs from a key row's (``None``: the same).  ``values_are_keys``: a position's value is
+    its key; one set of pages serves as both."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
+    values_are_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -316,10 +318,12 @@ class Norm(Part):
 @dataclass(frozen=True)
 class RotaryPlan:
     """A rotation by ``position * inv_freq[i]`` of ``rot_dims / 2`` pairs at the start of every head: pair i is
-    ``(2i, 2i + 1)`` when ``interleaved``, else ``(i, i + rot_dims / 2)``; dims from ``rot_dims`` on pass unchanged."""
+    ``(2i, 2i + 1)`` when ``interleaved``, else ``(i, i + rot_dims / 2)``; dims from ``rot_dims`` on pass unchanged.
+    With a ``magnitude`` other than 1 the rotated pairs are also scaled by it."""
     inv_freq: torch.Tensor          # fp32 [rot_dims / 2], on the device
     rot_dims: int
     interleaved: bool
+    magnitude: float = 1.0          # cos and sin are both multiplied by this
 
 
 class PositionEncoding(Part):

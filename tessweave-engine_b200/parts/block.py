@@ -214,3 +214,37 @@ class HyperPreNormBlock(ArrangedBlock):
         delta = self.feed_forward.forward(ctx, h)
         _, out2, mix2 = self._coef(1)
         stream.pending = (dense_delta(ctx, delta, dt, "hyper.y")[:n], mix2, out2)
+
+
+@register_part("block", "parallel_pre_norm")
+class ParallelPreNormBlock(ArrangedBlock):
+    """x = x + (mixer(norm1(x)) + feed_forward(norm1(x))): one norm, and both sub-layers read its output.
+    ``feed_forward`` may be None: the layer then has its mixer only.
+
+    The mixer's delta is added to the fp32 residual rows right away (nothing reads them before the next norm); the
+    feed-forward's is left pending, so the next norm's kernel adds it while it normalises.
+    """
+
+    ROLES = ("norm1", "mixer", "feed_forward")
+
+    def __init__(self, runtime: Runtime, hidden: int, norm1: PartSpec, mixer: PartSpec, feed_forward: PartSpec | None = None,
+                 names: dict[str, str] | None = None):
+        super().__init__(runtime, hidden, names)
+        self.norm1 = build_part("norm", norm1, runtime)
+        self.mixer = build_part("mixer", mixer, runtime)
+        self.feed_forward = build_part("feed_forward", feed_forward, runtime) if feed_forward is not None else None
+        self.graph_safe = all(p.graph_safe for p in self.parts().values())
+
+    def forward(self, ctx: StepContext, stream: ResidualStream, cache, write_cache: bool) -> None:
+        n, dt = ctx.n_tokens, self.runtime.dtype
+        stream.rounded = None
+        h = ctx.workspace.get("block.h", (n, self.hidden), dt)
+        self.norm1.apply(ctx, h, stream.resid, stream.pending, n)
+        ctx.upcoming_weights = self.feed_forward.streamed_first() if self.feed_forward is not None else None
+        delta = self.mixer.forward(ctx, h, cache, write_cache)
+        ctx.upcoming_weights = None
+        if self.feed_forward is None:
+            stream.pending = delta
+            return
+        ops.add_delta(stream.resid, delta, n)
+        stream.pending = self.feed_forward.forward(ctx, h)

@@ -15,10 +15,20 @@ class WeightedSumMixer(Mixer):
     ``members``: (checkpoint prefix, mixer spec, scale) per member, in order.  Each member keeps the cache or
     state it needs itself (``SeveralNeeds`` / ``SeveralViews``, in the members' order); the sum is formed in fp32
     and rounded once.
+
+    With ``member_norm_eps`` every member's result is first divided by its root mean square over the width (eps
+    inside the root) and multiplied by a learned weight of its own, ``<prefix>.<member_norm_name>``:
+    delta = sum_m scale_m * rms(mixer_m(h)) * w_m, statistics and products in fp32.
     """
 
-    def __init__(self, runtime: Runtime, hidden: int, members: tuple):
+    def __init__(self, runtime: Runtime, hidden: int, members: tuple, member_norm_eps: float | None = None,
+                 member_norm_name: str = "norm"):
         super().__init__(runtime)
+        if member_norm_eps is not None and not member_norm_eps > 0:
+            raise ValueError("weighted_sum: member_norm_eps must be positive")
+        self.norm_eps, self.norm_name = member_norm_eps, member_norm_name
+        self.norm_weights = (runtime.empty(len(members), hidden, dtype=torch.float32)
+                             if member_norm_eps is not None else None)
         if not members:
             raise ValueError("weighted_sum: at least one member")
         self.hidden = hidden
@@ -28,8 +38,12 @@ class WeightedSumMixer(Mixer):
         self.graph_safe = all(m.graph_safe for m in self.members)
 
     def weights(self) -> list[WeightDecl]:
-        return [WeightDecl(join_name(prefix, w.name), w.shape, w.role, w.init, w.dest)
-                for prefix, member in zip(self.prefixes, self.members) for w in member.weights()]
+        decls = [WeightDecl(join_name(prefix, w.name), w.shape, w.role, w.init, w.dest)
+                 for prefix, member in zip(self.prefixes, self.members) for w in member.weights()]
+        if self.norm_weights is not None:
+            decls += [WeightDecl(join_name(prefix, self.norm_name), (self.hidden,), role="vector", init="one_plus_normal",
+                                 dest=self.norm_weights[i]) for i, prefix in enumerate(self.prefixes)]
+        return decls
 
     def redundant_names(self) -> list[str]:
         return [join_name(prefix, n) for prefix, member in zip(self.prefixes, self.members) for n in member.redundant_names()]
@@ -50,5 +64,9 @@ class WeightedSumMixer(Mixer):
         last = len(self.members) - 1
         for i, (member, scale, view) in enumerate(zip(self.members, self.scales, cache.views)):
             delta = dense_delta(ctx, member.forward(ctx, h, view, write_cache), dt)[:n]
-            ops.scaled_accumulate(acc, out if i == last else None, delta, scale, first=(i == 0))
+            if self.norm_weights is not None:
+                ops.normed_accumulate(acc, out if i == last else None, delta, self.norm_weights[i], self.norm_eps, scale,
+                                      first=(i == 0), n_rows=n)
+            else:
+                ops.scaled_accumulate(acc, out if i == last else None, delta, scale, first=(i == 0))
         return out

@@ -1,6 +1,8 @@
 """Position encodings."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..csrc import ops
@@ -17,10 +19,23 @@ class RotaryEmbedding(PositionEncoding):
     uploaded once per head size, so the device only multiplies by the position.  Values of a head from
     ``dims`` on pass unchanged; only the whole-head form has kernels that rotate on the way
     (``fused_rotary_table``).
+
+    ``yarn`` (``factor``, ``original``, ``fast``, ``slow``) stretches the slow frequencies for contexts beyond the
+    ``original`` length: with d(t) = dims * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
+    hi = min(ceil(d(slow)), dims - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at
+    inv_freq[i] / factor * r_i + inv_freq[i] * (1 - r_i), and cos and sin are both multiplied by
+    0.1 * ln(factor) + 1 (``magnitude``).  The table is made on the host in double precision and rounded once.
     """
 
-    def __init__(self, runtime: Runtime, theta: float, dims: int | None = None):
+    def __init__(self, runtime: Runtime, theta: float, dims: int | None = None, yarn: dict | None = None):
         super().__init__(runtime)
+        self.yarn = None
+        self.magnitude = 1.0
+        if yarn is not None:
+            self.yarn = {k: float(yarn[k]) for k in ("factor", "original", "fast", "slow")}
+            if min(self.yarn.values()) <= 0 or not theta > 1:
+                raise ValueError("rope: yarn needs positive factor, original, fast and slow, and theta above 1")
+            self.magnitude = 0.1 * math.log(self.yarn["factor"]) + 1.0
         if not theta > 0:
             raise ValueError("rope theta must be positive")
         if dims is not None and (dims < 0 or dims % 2):
@@ -33,10 +48,28 @@ class RotaryEmbedding(PositionEncoding):
         if table is None:
             if dims % 2:
                 raise ValueError(f"rope needs an even number of rotated dims, got {dims}")
-            inv = self.theta ** (-torch.arange(0, dims, 2, dtype=torch.float32) / max(dims, 1))
+            if self.yarn is None:
+                inv = self.theta ** (-torch.arange(0, dims, 2, dtype=torch.float32) / max(dims, 1))
+            else:
+                inv = torch.tensor(self._yarn_frequencies(dims), dtype=torch.float64).to(torch.float32)
             table = inv.to(self.runtime.device)
             self._tables[dims] = table
         return table
+
+    def _yarn_frequencies(self, dims: int) -> list[float]:
+        y = self.yarn
+
+        def pair_turning(t: float) -> float:        # the (fractional) pair that makes t turns over the original length
+            return dims * math.log(y["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(pair_turning(y["fast"])), 0)
+        hi = min(math.ceil(pair_turning(y["slow"])), dims - 1)
+        out = []
+        for i in range(dims // 2):
+            f = self.theta ** (-2.0 * i / dims)
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / y["factor"] * ramp + f * (1.0 - ramp))
+        return out
 
     def _dims(self, head_dim: int) -> int:
         dims = head_dim if self.dims is None else self.dims
@@ -45,20 +78,22 @@ class RotaryEmbedding(PositionEncoding):
         return dims
 
     def fused_rotary_table(self, head_dim: int) -> torch.Tensor | None:
-        return self._table(head_dim) if self._dims(head_dim) == head_dim else None
+        # the kernels that rotate on the way know no magnitude
+        return self._table(head_dim) if self._dims(head_dim) == head_dim and self.magnitude == 1.0 else None
 
     def rotary_plan(self, head_dim: int) -> RotaryPlan:
         dims = self._dims(head_dim)
-        return RotaryPlan(self._table(dims), dims, interleaved=False)
+        return RotaryPlan(self._table(dims), dims, interleaved=False, magnitude=self.magnitude)
 
     def apply(self, ctx: StepContext, qk: torch.Tensor, n_heads: int, head_dim: int) -> None:
         """Rotate ``n_heads`` heads at the start of each packed row in place (nothing else is touched).
         A mixer with a kernel that rotates on the way (``fused_rotary_table``) gets the same numbers."""
         dims = self._dims(head_dim)
-        if dims == head_dim:
+        if dims == head_dim and self.magnitude == 1.0:
             ops.rotate_heads(qk, None, ctx.positions, ctx.seq_of_token, self._table(dims), ctx.n_tokens, n_heads, head_dim)
         elif dims:
-            ops.rotate_pairs(qk, ctx.positions, ctx.seq_of_token, self._table(dims), ctx.n_tokens, n_heads, head_dim, dims, False)
+            ops.rotate_pairs(qk, ctx.positions, ctx.seq_of_token, self._table(dims), ctx.n_tokens, n_heads, head_dim, dims, False,
+                             magnitude=self.magnitude)
 
 
 @register_part("position", "rope_interleaved")

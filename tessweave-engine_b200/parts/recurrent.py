@@ -153,7 +153,7 @@ class Retention(MatrixStateMixer):
         proj = linear(ctx, "retention.in", h, self.w_in)
         plan = self.position.rotary_plan(self.key_dim) if self.position is not None else None
         rotate = {}
-        if plan is not None and not plan.interleaved:
+        if plan is not None and not plan.interleaved and plan.magnitude == 1.0:
             rotate = {"inv_freq": plan.inv_freq, "rot_dims": plan.rot_dims}
         elif self.position is not None:
             self.position.apply(ctx, proj, 2 * self.n_heads, self.key_dim)
@@ -282,3 +282,114 @@ class MLSTM(MatrixStateMixer):
         raw, den = self._recur(ctx, proj[:, :a], proj[:, a:2 * a], proj[:, 2 * a:2 * a + b], cache, write_cache,
                                pre=gates, p0=self.b_gates, q_scale=self.key_dim ** -0.5, cap=self.gate_cap)
         return self._finish(ctx, raw, den, self.norm, proj[:, 2 * a + b:])
+
+
+@register_part("mixer", "gated_delta")
+class GatedDelta(MatrixStateMixer):
+    """The gated delta rule: a matrix memory that decays, then is corrected towards the token's value.
+
+        q, k = Wq h, Wk h   (n_qk_heads heads of key_dim);   v = Wv h   (n_heads heads of value_dim)
+        each of q, k, v: a causal convolution over time per channel (``conv_taps`` taps, zeros before the start), then silu
+        q <- q / sqrt(sum q^2 + 1e-6) * key_dim^-1/2,  k <- k / sqrt(sum k^2 + 1e-6)          per head, fp32
+        beta = sigmoid(Wb h)                                                                per head
+        g = exp(-exp(A_h) softplus(d + dt_bias))       d = Wa h per head, or with ``channel_decay`` Wa2 (Wa1 h) per head
+                                                       and key channel (inner size ``decay_rank``)
+        S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q                  fp32, S zero at the start
+        delta = (rms_head(o) * norm * act(gate)) Wo^T        gate = Wg h, or with ``gate_rank`` Wg2 (Wg1 h); ``gate`` names
+                                                       the activation (silu or sigmoid); norm [value_dim] serves every head
+
+    Value head h reads q/k head h // (n_heads / n_qk_heads).  The state slot holds S of every head and, behind them, the
+    last ``conv_taps - 1`` inputs of every convolved channel, so a request may be cut into steps anywhere.
+    Tensor names: q, k, v (each with ``.conv`` [channels, taps]), b, A_log, dt_bias, norm, o, and a, g or a1, a2, g1, g2.
+    """
+
+    rule = ops.RECURRENCE_DELTA
+    UNIT_EPS = 1e-6
+
+    def __init__(self, runtime: Runtime, hidden: int, n_heads: int, n_qk_heads: int, key_dim: int, value_dim: int,
+                 conv_taps: int, eps: float, channel_decay: bool = False, decay_rank: int | None = None, gate: str = "silu",
+                 gate_rank: int | None = None):
+        super().__init__(runtime)
+        self._sizes(hidden, n_heads, key_dim, value_dim, eps)
+        if n_qk_heads <= 0 or n_heads % n_qk_heads:
+            raise ValueError("gated_delta: n_heads must be a multiple of n_qk_heads")
+        if not 1 <= conv_taps <= ops.SHORT_CONV_MAX_TAPS:
+            raise ValueError(f"gated_delta: conv_taps must lie in 1..{ops.SHORT_CONV_MAX_TAPS}")
+        if gate not in ("silu", "sigmoid"):
+            raise ValueError(f"gated_delta: unknown gate activation {gate!r}")
+        if channel_decay and not decay_rank:
+            raise ValueError("gated_delta: a decay per channel needs the inner size of its projection (decay_rank)")
+        self.gate_act = ops.GATE_SILU if gate == "silu" else ops.GATE_SIGMOID
+        self.n_qk_heads, self.taps = int(n_qk_heads), int(conv_taps)
+        self.channel_decay = bool(channel_decay)
+        self.decay_rank = int(decay_rank) if channel_decay else None
+        self.gate_rank = int(gate_rank) if gate_rank else None
+        self.qk_size = n_qk_heads * key_dim                      # (the base class counted a q/k head per value head)
+        self.conv_channels = 2 * self.qk_size + self.v_size
+        self.conv_offset = self.state_numel                      # where the convolutions' last inputs sit in a slot
+        self.state_numel += self.conv_channels * (self.taps - 1)
+        # rows [Wq; Wk; Wv] and, where the gate is projected directly, [Wg] behind them
+        self.w_in = runtime.empty(self.conv_channels + (0 if self.gate_rank else self.v_size), hidden)
+        self.conv = runtime.empty(self.conv_channels, self.taps, dtype=torch.float32)
+        # the numbers that enter the recurrence in fp32: rows [Wb] and, where the decay is projected directly, [Wa]
+        self.w_small = runtime.empty(n_heads * (1 if self.channel_decay else 2), hidden)
+        self.w_a1 = runtime.empty(self.decay_rank, hidden) if self.channel_decay else None
+        self.w_a2 = runtime.empty(n_heads * key_dim, self.decay_rank) if self.channel_decay else None
+        self.w_g1 = runtime.empty(self.gate_rank, hidden) if self.gate_rank else None
+        self.w_g2 = runtime.empty(self.v_size, self.gate_rank) if self.gate_rank else None
+        self.rate_log = runtime.empty(n_heads, dtype=torch.float32)
+        self.dt_bias = runtime.empty(n_heads * key_dim if self.channel_decay else n_heads, dtype=torch.float32)
+        self.norm = runtime.empty(value_dim, dtype=torch.float32)
+        self.norm_per_head = runtime.empty(self.v_size, dtype=torch.float32)
+        self.w_o = runtime.empty(hidden, self.v_size)
+
+    def weights(self) -> list[WeightDecl]:
+        a, b, H, hid = self.qk_size, self.v_size, self.n_heads, self.hidden
+        spans = (("q", 0, a), ("k", a, 2 * a), ("v", 2 * a, 2 * a + b))
+        decls = [WeightDecl(n, (e - s, hid), dest=self.w_in[s:e]) for n, s, e in spans]
+        decls += [WeightDecl(f"{n}.conv", (e - s, self.taps), role="vector", init="wide_normal", dest=self.conv[s:e]) for n, s, e in spans]
+        decls += [WeightDecl("b", (H, hid), dest=self.w_small[:H]),
+                  WeightDecl("A_log", (H,), role="vector", dest=self.rate_log),
+                  WeightDecl("dt_bias", (self.dt_bias.numel(),), role="vector", dest=self.dt_bias),
+                  WeightDecl("norm", (self.value_dim,), role="vector", init="one_plus_normal", dest=self.norm),
+                  WeightDecl("o", (hid, b), dest=self.w_o)]
+        if self.channel_decay:
+            decls += [WeightDecl("a1", (self.decay_rank, hid), dest=self.w_a1),
+                      WeightDecl("a2", (H * self.key_dim, self.decay_rank), dest=self.w_a2)]
+        else:
+            decls.append(WeightDecl("a", (H, hid), dest=self.w_small[H:]))
+        if self.gate_rank:
+            decls += [WeightDecl("g1", (self.gate_rank, hid), dest=self.w_g1), WeightDecl("g2", (b, self.gate_rank), dest=self.w_g2)]
+        else:
+            decls.append(WeightDecl("g", (b, hid), dest=self.w_in[2 * a + b:]))
+        return decls
+
+    def finalize(self) -> None:
+        self.norm_per_head.view(self.n_heads, self.value_dim).copy_(self.norm.expand(self.n_heads, self.value_dim))
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
+        cache = self._check(cache)
+        n, ws, H = ctx.n_tokens, ctx.workspace, self.n_heads
+        a, b, C = self.qk_size, self.v_size, self.conv_channels
+        proj = linear(ctx, "delta.in", h, self.w_in)
+        small = linear(ctx, "delta.small", h, self.w_small, out_dtype=torch.float32)
+        if self.channel_decay:
+            decay = linear(ctx, "delta.a2", linear(ctx, "delta.a1", h, self.w_a1), self.w_a2, out_dtype=torch.float32)
+        else:
+            decay = small[:, H:]
+        if self.gate_rank:
+            gate = linear(ctx, "delta.g2", linear(ctx, "delta.g1", h, self.w_g1), self.w_g2)
+        else:
+            gate = proj[:, C:]
+        # convolution, activation and unit length in one pass over the row; q's heads come first and carry the scale
+        ready = ws.get("delta.ready", (n, C), torch.float32)
+        ops.short_conv(ready, proj, self.conv, cache.state, self.conv_offset, ctx.seq_of_token, ctx.seq_slot, ctx.seq_q_start, n,
+                       unit_heads=2 * self.n_qk_heads, unit_dim=self.key_dim, scaled_heads=self.n_qk_heads,
+                       head_scale=self.key_dim ** -0.5, unit_eps=self.UNIT_EPS)
+        if write_cache and self.taps > 1:
+            ops.short_conv_state(proj, self.taps, C, cache.state, self.conv_offset, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len,
+                                 ctx.n_seqs)
+        raw, _ = self._recur(ctx, ready[:, :a], ready[:, a:2 * a], ready[:, 2 * a:], cache, write_cache, pre=decay,
+                             p0=self.rate_log, p1=self.dt_bias, write_pre=small, channel_decay=self.channel_decay,
+                             qk_group=H // self.n_qk_heads)
+        return self._finish(ctx, raw, None, self.norm_per_head, gate)

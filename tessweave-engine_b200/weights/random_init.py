@@ -3,7 +3,7 @@
 Every tensor is drawn on the CPU from its own generator, seeded by (seed, tensor
 name), so any subset of tensors can be reproduced alone.  The rule per tensor is
 the declaration's: matrices, embeddings and biases ~ N(0, std); norm weights
-~ 1 + N(0, 0.1); square matrices that mix heads ~ I + N(0, std).  The reference has no such mode (its tests take random weights
+~ 1 + N(0, 0.1); taps of short convolutions ~ N(0, 0.4); square matrices that mix heads ~ I + N(0, std).  The reference has no such mode (its tests take random weights
 from a library model: tests/test_engine.py:15-25).
 
 ``fill_random`` draws the same kind of weights straight into a model's device
@@ -23,6 +23,7 @@ from ..models.model import Model
 from ..parts.base import Runtime, WeightDecl
 
 NORM_WEIGHT_STD = 0.1
+WIDE_STD = 0.4        # taps of short convolutions: a few numbers per channel that must not shrink what passes
 
 
 def tensor_seed(seed: int, name: str) -> int:
@@ -42,6 +43,8 @@ def draw(decl: WeightDecl, seed: int, std: float) -> torch.Tensor:
         return 1.0 + NORM_WEIGHT_STD * noise
     if decl.init == "normal":
         return std * noise
+    if decl.init == "wide_normal":
+        return WIDE_STD * noise
     if decl.init == "eye_plus_normal":
         return torch.eye(decl.shape[0], decl.shape[1]) + std * noise
     raise ValueError(f"unknown init rule {decl.init!r} for {decl.name}")
@@ -97,6 +100,9 @@ def fill_random(model: Model, seed: int = 0, std: float | None = None) -> Model:
         for begin in range(0, rows, step):      # in slabs, so no second full-size copy is alive
             part = decl.dest[begin:begin + step]
             noise = torch.randn(part.shape, generator=g, device=device, dtype=torch.float32)
-            part.copy_(1.0 + NORM_WEIGHT_STD * noise if decl.init == "one_plus_normal" else std * noise)
+            if decl.init == "one_plus_normal":
+                part.copy_(1.0 + NORM_WEIGHT_STD * noise)
+            else:
+                part.copy_((WIDE_STD if decl.init == "wide_normal" else std) * noise)
     model.finalize()
     return model
