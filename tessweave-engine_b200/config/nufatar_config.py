@@ -83,8 +83,8 @@ class SoftmaxAttentionConfig:
         vdim = _positive_int(_need(d, "vdim", where), f"{where}.vdim")
         if heads % kv_heads:
             raise ConfigError(f"config.json: {where}: heads must be a multiple of kv_heads")
-        if dim % 2 or max(dim, vdim) > 256:
-            raise ConfigError(f"config.json: {where}: head sizes must be even and at most 256")
+        if max(dim, vdim) > 256:
+            raise ConfigError(f"config.json: {where}: head sizes above 256 are not supported")
         scale = _finite(_need(d, "scale", where), f"{where}.scale")
         if kind == "parallel":
             window = _positive_int(_need(_need(d, "mask", where), "size", f"{where}.mask"), f"{where}.mask.size")
@@ -214,7 +214,7 @@ class NufatarConfig:
                     raise ConfigError("config.json: loop.start, loop.stop and loop.times must be integers")
             if not (0 <= start <= stop <= len(layers)) or times < 1:
                 raise ConfigError(f"config.json: loop: 0 <= start <= stop <= {len(layers)} and times >= 1 are required")
-            loop = LoopConfig(start, stop, times) if stop > start else None
+            loop = LoopConfig(start, stop, times)
         cfg = cls(architecture=str(d.get("architecture", "Nufatar")),
                   vocab=_positive_int(_need(d, "vocab", "the top level"), "vocab"),
                   width=_positive_int(_need(d, "width", "the top level"), "width"),

@@ -75,7 +75,7 @@ def nufatar_spec(cfg: NufatarConfig) -> ModelSpec:
                                                          "names": ("gate", "up", "down")})
         layers.append(LayerSpec(PartSpec("parallel_pre_norm", params), f"l{i}"))
     n, loop = len(layers), cfg.loop
-    if loop is None:
+    if loop is None or loop.stop <= loop.start:      # (an empty range: the pass vectors are loaded and nothing reads them)
         schedule = [ScheduleEntry(i) for i in range(n)]
     else:
         schedule = [ScheduleEntry(i) for i in range(loop.start)]

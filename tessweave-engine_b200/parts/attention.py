@@ -109,10 +109,10 @@ class GQAAttention(Mixer):
         spans = (("q", 0, q), ("k", q, q + kv)) + ((("v", q + kv, self.qkv_width),) if not self.values_are_keys else ())
         extra = []
         if self.sink is not None:
-            extra.append(WeightDecl(self.sink_name, (self.n_heads,), role="vector", dest=self.sink))
+            extra.append(WeightDecl(self.sink_name, (self.n_heads,), role="vector", init="wide_normal", dest=self.sink))
         if self.distance_bias is not None:
             extra.append(WeightDecl(self.distance_bias["name"], (self.distance_bias["rows"], self.n_heads), role="vector",
-                                    dest=self.bias_table))
+                                    init="wide_normal", dest=self.bias_table))
         decls = [WeightDecl(nm[n], (e - b, self.hidden), dest=self.w_qkv[b:e]) for n, b, e in spans]
         if self.b_qkv is not None:
             decls += [WeightDecl(nm[f"{n}_bias"], (e - b,), role="vector", dest=self.b_qkv[b:e]) for n, b, e in spans]
