@@ -331,3 +331,163 @@ def sapatar_kernel_table(config: dict, batch: int, context: int, prefill_tokens:
     if int(status) != 0:
         raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
     return rows
+
+
+# ---------------------------------------------------------------------------
+# the Nufatar decoder
+# ---------------------------------------------------------------------------
+def nufatar_config_like(qwen: dict, layers: int) -> dict:
+    """A Nufatar config.json with the sizes of the Qwen2 configuration ``qwen``: layers [causal, windowed, causal,
+    causal] in turn, all of them with the dense feed-forward of ``qwen``.  Both attentions have Qwen2's head counts and
+    head size (the causal one rotates half of a head at stretched rates; the windowed one sees 1,024 tokens through a
+    distance table of 32 rows that reaches 512); the delta rules have half as many heads of the same size, a q/k head
+    for every two of them and convolutions of four taps; the low-rank projections have an inner size of 64.  The first
+    half of the layers is run twice."""
+    heads, kv, dim, width = qwen["num_attention_heads"], qwen["num_key_value_heads"], qwen["head_dim"], qwen["hidden_size"]
+    half = max(2, heads // 2)
+    mlp = {"kind": "dense", "ff": qwen["intermediate_size"]}
+    right = {"heads": half, "kv_heads": half // 2, "dim": dim, "vdim": dim, "conv": 4}
+    causal = {"type": "parallel_2", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "rot": {"dims": dim // 2, "base": qwen["rope_theta"],
+                         "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        "right": right, "left_scale": 0.6, "right_scale": 1.1}}
+    windowed = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": 1024},
+                 "bias_max": 512, "bias_rows": 32},
+        "right": {**right, "decay_rank": 64, "gate_rank": 64}}}
+    pattern = [causal, windowed, causal, causal]
+    return {"architecture": "Nufatar", "vocab": qwen["vocab_size"], "width": width, "norm": {"eps": qwen["rms_norm_eps"]},
+            "layers": [pattern[i % 4] for i in range(layers)], "loop": {"start": 0, "stop": max(1, layers // 2), "times": 2}}
+
+
+def nufatar_kernel_table(config: dict, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, tflops: float,
+                         page_size: int = 16) -> list[dict]:
+    """The Nufatar kernels alone, each inside a CUDA graph with operands rotated beyond L2, for a decode step of
+    ``batch`` rows and a prompt step: both attentions over their caches (position encoding, store and attention), the
+    short convolutions with their unit norms, the delta rule with either kind of decay, the norm over heads with its
+    gate, and the normalised sum of the two sides.  fraction = max(bytes / HBM peak, FLOPs / tensor peak) / time."""
+    import tessweave_engine_b200 as tw
+    from ..models.nufatar import attention_spec
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    rt = Runtime(dev, bf)
+    cfg, _ = tw.resolve(config)
+    W = cfg.width
+    causal = next(l.mixer for l in cfg.layers if l.type == "parallel_2")
+    windowed = next(l.mixer for l in cfg.layers if l.type == "parallel")
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows: list[dict] = []
+
+    def add(name, m, thunks, nbytes, flops, reps=4, note=""):
+        kernel = _kernels_of(thunks[0])
+        us = _graph_us(thunks, reps)
+        floor = max(nbytes / (hbm_gbs * 1e9), flops / (tflops * 1e12)) * 1e6
+        rows.append({"op": name, "rows": m, "kernel": kernel, "us": round(us, 2), "mbytes": round(nbytes / 1e6, 2),
+                     "gflop": round(flops / 1e9, 2), "floor_us": round(floor, 2), "frac": round(floor / us, 3),
+                     "bound": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (tflops * 1e12) else "tensor", "note": note})
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)     # noqa: E731
+    for m, phase in ((batch, "decode"), (prefill_tokens, "prefill")):
+        requests = batch if phase == "decode" else 1
+        per = m // requests
+        slots, starts, lens = i32(list(range(requests))), i32([r * per for r in range(requests)]), i32([per] * requests)
+        seq_of = i32([r for r in range(requests) for _ in range(per)])
+        positions = i32([context - 1] * m if phase == "decode" else list(range(m)))
+        ws = Workspace(dev)
+        ctx = _context(rt, ws, status, positions.tolist(), seq_of.tolist(), list(range(requests)), starts.tolist(), lens.tolist(),
+                       [context] * requests if phase == "decode" else [m])
+        # ---- the two attentions: position encoding, store, attention
+        for label, side in (("causal attention, half of a head rotated", causal.left),
+                            (f"attention over a window of {windowed.left.window} with distance table and sink, values = keys", windowed.left)):
+            att = build_part("mixer", attention_spec(cfg, side, "bench"), rt)
+            _fill(att)
+            att.finalize()
+            Hq, G, D = att.n_heads, att.n_kv_heads, att.head_dim
+            kv_tokens = context if phase == "decode" else m
+            seen = min(kv_tokens, side.window) if side.window else kv_tokens
+            blocks = -(-kv_tokens // page_size)
+            per_key = G * D * 2 * (1 if att.values_are_keys else 2)
+            caches = []
+            for _ in range(_copies(requests * blocks * page_size * per_key)):
+                cache = CacheManager([(att.cache_need(), None)], page_size, requests * blocks, requests, kv_tokens, bf, dev,
+                                     prefix_cache=False)
+                for g in cache.groups:
+                    g.k.normal_(0, 0.5)
+                    if g.v is not g.k:
+                        g.v.normal_(0, 0.5)
+                for _r in range(requests):
+                    cache.ensure(cache.admit(None), kv_tokens)
+                cache.sync_tables()
+                caches.append(cache)
+            views = [c.view(0) for c in caches]
+            projs = [torch.randn(m, att.qkv_width, device=dev, dtype=bf) for _ in range(_copies(m * att.qkv_width * 2) if phase == "prefill" else 1)]
+            if phase == "decode":
+                nbytes = m * seen * per_key + m * (att.qkv_width + att.out_size) * 2
+                flops = 2.0 * m * Hq * 2 * D * seen
+            else:
+                nbytes = m * (att.qkv_width * 2 + att.out_size) * 2 + m * per_key
+                pairs = m * (m + 1) / 2 if not side.window else seen * (m - seen) + seen * (seen + 1) / 2
+                flops = 2.0 * Hq * 2 * D * pairs
+            add(f"{phase}: {label}", m,
+                [(lambda v=v, i=i: att.attend(ctx, projs[i % len(projs)], v, True)) for i, v in enumerate(views)], nbytes, flops,
+                reps=2 if phase == "prefill" else 4)
+            del caches, views, projs, att
+            torch.cuda.empty_cache()
+        # ---- the delta rule: convolutions, recurrence, norm over heads
+        for label, side in (("a decay per head", causal.right), ("a decay per key channel", windowed.right)):
+            H, Gq, Dk, Dv, taps = side.heads, side.kv_heads, side.dim, side.vdim, side.conv
+            C = 2 * Gq * Dk + H * Dv
+            numel = ops.recurrence_state_numel(ops.RECURRENCE_DELTA, H, Dk, Dv)
+            conv_w = torch.randn(C, taps, device=dev) * 0.3
+            n_sets = _copies(max(requests * numel * 8, m * C * 6))
+            sets = []
+            for _ in range(n_sets):
+                state = torch.zeros(requests, numel + C * (taps - 1), device=dev)
+                sets.append((torch.randn(m, C, device=dev, dtype=bf) * 0.3, torch.empty(m, C, device=dev), state,
+                             torch.empty(m, H * Dv, device=dev), torch.randn(m, 2 * H, device=dev),
+                             torch.randn(m, H * Dk, device=dev) if side.channel_decay else None))
+            if label == "a decay per head":
+                def conv(s):
+                    ops.short_conv(s[1], s[0], conv_w, s[2], numel, seq_of, slots, starts, m, unit_heads=2 * Gq, unit_dim=Dk,
+                                   scaled_heads=Gq, head_scale=Dk ** -0.5, unit_eps=1e-6)
+                    ops.short_conv_state(s[0], taps, C, s[2], numel, slots, starts, lens, requests)
+                add(f"{phase}: convolutions of {taps} taps + silu + unit norms, {C} channels", m, [(lambda s=s: conv(s)) for s in sets],
+                    m * C * 6 + 2 * requests * C * (taps - 1) * 4, 0.0, reps=8)
+            for s in sets:
+                s[1].normal_(0, 0.1)
+            rate = torch.full((H,), -1.0, device=dev)
+            dt = torch.zeros(H * Dk if side.channel_decay else H, device=dev)
+            a = Gq * Dk
+
+            def recur(s):
+                ops.linear_recurrence(ops.RECURRENCE_DELTA, s[3], None, s[1][:, :a], s[1][:, a:2 * a], s[1][:, 2 * a:], s[2], positions,
+                                      slots, starts, lens, requests, H, Dk, Dv, True, pre=s[5] if side.channel_decay else s[4][:, H:],
+                                      p0=rate, p1=dt, write_pre=s[4], channel_decay=side.channel_decay, qk_group=H // Gq, max_q_len=per)
+            nbytes = m * C * 4 + m * H * Dv * 4 + 2 * requests * numel * 4 + (m * H * Dk * 4 if side.channel_decay else m * H * 8)
+            add(f"{phase}: delta rule with {label}, {H} heads of {Dk} x {Dv}", m, [(lambda s=s: recur(s)) for s in sets], nbytes, 0.0,
+                reps=2 if phase == "prefill" else 8,
+                note=f"{6.0 * m * H * Dk * Dv / 1e9:.2f} GFLOP of fp32 multiply-adds outside the tensor cores")
+            del sets
+            torch.cuda.empty_cache()
+        H, Dv = causal.right.heads, causal.right.vdim
+        sets = [(torch.randn(m, H * Dv, device=dev), torch.randn(m, H * Dv, device=dev, dtype=bf), torch.empty(m, H * Dv, device=dev, dtype=bf))
+                for _ in range(_copies(m * H * Dv * 8))]
+        nw = torch.ones(H * Dv, device=dev)
+        add(f"{phase}: norm over each head + gate", m,
+            [(lambda r=r, g=g, o=o: ops.head_norm_gate(o, r, None, nw, g, ops.GATE_SILU, 1e-6, m, H, Dv)) for r, g, o in sets],
+            m * H * Dv * 8, 0.0, reps=8)
+        del sets
+        # ---- the normalised sum of the two sides
+        sets = [(torch.empty(m, W, device=dev), torch.empty(m, W, device=dev, dtype=bf), torch.randn(m, W, device=dev, dtype=bf),
+                 torch.randn(m, W, device=dev, dtype=bf)) for _ in range(_copies(m * W * 14))]
+        nw = torch.ones(W, device=dev)
+
+        def both(acc, out, x, y):
+            ops.normed_accumulate(acc, None, x, nw, 1e-6, 0.5, first=True, n_rows=m)
+            ops.normed_accumulate(acc, out, y, nw, 1e-6, 0.5, first=False, n_rows=m)
+        add(f"{phase}: RMSNorm of each side + half their sum", m, [(lambda s=s: both(*s)) for s in sets], m * W * (2 + 4 + 2 + 4 + 4 + 2), 0.0, reps=8)
+        del sets
+        torch.cuda.empty_cache()
+    if int(status) != 0:
+        raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
+    return rows

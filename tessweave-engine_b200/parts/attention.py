@@ -49,8 +49,8 @@ class GQAAttention(Mixer):
         super().__init__(runtime)
         if min(hidden, n_heads, n_kv_heads, head_dim) <= 0 or n_heads % n_kv_heads:
             raise ValueError("attention: heads must be positive and n_heads a multiple of n_kv_heads")
-        if head_dim % 2 or head_dim > 256:
-            raise ValueError(f"attention: head_dim {head_dim} must be even and at most 256")
+        if (head_dim % 2 and position.kind != "none") or head_dim > 256:
+            raise ValueError(f"attention: head_dim {head_dim} must be at most 256, and even where heads are rotated")
         if out_bias:
             raise ValueError("attention: a bias on the output projection is not implemented")
         if window is not None and window <= 0:

@@ -191,3 +191,53 @@ def test_generate_sapatar_as_a_user_starts_it(tmp_path):
     assert proc.returncode == 0, proc.stderr[-3000:]
     got = [int(t) for t in proc.stdout.strip().split(",")]
     assert got == plain_sapatar.greedy(folder, prompt, 8)
+
+
+# ---------------------------------------------------------------------------
+# the Nufatar decoder through the same command line
+# ---------------------------------------------------------------------------
+def test_doctor_and_inspect_know_nufatar(tmp_path):
+    import plain_nufatar
+    from tiny_nufatar import NUFATAR_A
+    assert "Nufatar" in json.loads(run_cli("doctor").stdout)["architectures"]
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(NUFATAR_A))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 2, "--init-std", 0.1).returncode == 0
+    proc = run_cli("inspect", folder, "--kv-blocks", 10, "--block-size", 8)
+    assert proc.returncode == 0, proc.stderr
+    out = json.loads(proc.stdout)
+    runs = plain_nufatar.layer_runs(NUFATAR_A)
+    per_token = states = 0
+    for i, _ in runs:                                     # every run of a repeated layer keeps pages and a state of its own
+        m = NUFATAR_A["layers"][i]["mixer"]
+        lft, rgt = m["left"], m["right"]
+        per_token += lft["kv_heads"] * (lft["dim"] + (lft["vdim"] if "rot" in lft else 0))       # values that are the keys cost nothing
+        channels = 2 * rgt["kv_heads"] * rgt["dim"] + rgt["heads"] * rgt["vdim"]
+        states += rgt["heads"] * rgt["dim"] * rgt["vdim"] + channels * (rgt["conv"] - 1)
+    assert out["layers_in_schedule"] == len(runs) == 8
+    assert out["kv_bf16_bytes"] == per_token * 2 * 10 * 8
+    assert out["state_bytes_per_request"] == 4 * states
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps({**NUFATAR_A, "layers": [{**NUFATAR_A["layers"][0], "type": "parallel_3"}]}))
+    proc = run_cli("inspect", bad)
+    assert proc.returncode != 0 and "not implemented" in proc.stderr
+
+
+@pytest.mark.gpu
+def test_generate_nufatar_as_a_user_starts_it(tmp_path):
+    """init -> generate --prompt-ids in float32 -> the plain implementation's greedy continuation."""
+    import plain_nufatar
+    from tiny_nufatar import NUFATAR_D
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(NUFATAR_D))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 11, "--init-std", 0.25).returncode == 0
+    prompt = [5, 17, 3, 20, 41, 7, 50, 10, 23]
+    proc = run_cli("generate", folder, "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32", "--max-tokens", 8,
+                   "--ignore-eos", "--log", tmp_path / "runs" / "engine.jsonl", "--block-size", 8, "--kv-blocks", 32,
+                   "--prefill-chunk", 4, "--max-context", 256)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    got = [int(t) for t in proc.stdout.strip().split(",")]
+    assert got == plain_nufatar.greedy(folder, prompt, 8)
