@@ -118,7 +118,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                    const int* __restrict__ block_table, int table_stride, const bf16* k_cache,
                    const bf16* v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
                    float scale_log2e, int nsplit, float* __restrict__ partial_o, float* __restrict__ partial_ml,
-                   int* __restrict__ counters, int* status, const FusedQkv fq) {
+                   int* __restrict__ counters, int* status, const FusedQkv fq, const ScoreTerms terms) {
     // k_cache and v_cache carry no __restrict__: with FUSED the block that holds the newest position writes that
     // position's key and value through fq.k_cache / fq.v_cache, which are the same memory, and reads them back
     // below: that one key row with ld.global.cg (L2, coherent) and the values with cp.async.cg, never through
@@ -362,6 +362,22 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
             sacc[1] = oka ? sacc[1] * scale_log2e : NEG_INF;
             sacc[2] = okb ? sacc[2] * scale_log2e : NEG_INF;
             sacc[3] = okb ? sacc[3] * scale_log2e : NEG_INF;
+            if (terms.bias) {
+                // the table's rows of heads 2c and 2c + 1 at the distances of keys g and g + 8 (heads beyond the
+                // group have a zero query and no output: any row will do for them)
+                const float* ba = terms.bias + (size_t)min(kvh * G + h0 + 2 * c, Hq - 1) * terms.reach;
+                const float* bb = terms.bias + (size_t)min(kvh * G + h0 + 2 * c + 1, Hq - 1) * terms.reach;
+                if (oka) {
+                    const int da = min(pos - (key0 + g), terms.reach - 1);
+                    sacc[0] = fmaf(__ldg(ba + da), LOG2E, sacc[0]);
+                    sacc[1] = fmaf(__ldg(bb + da), LOG2E, sacc[1]);
+                }
+                if (okb) {
+                    const int db = min(pos - (key0 + g + 8), terms.reach - 1);
+                    sacc[2] = fmaf(__ldg(ba + db), LOG2E, sacc[2]);
+                    sacc[3] = fmaf(__ldg(bb + db), LOG2E, sacc[3]);
+                }
+            }
             // maxima over the 16 keys: over the lanes that share c
             float r0 = fmaxf(sacc[0], sacc[2]), r1 = fmaxf(sacc[1], sacc[3]);
 #pragma unroll
@@ -449,6 +465,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         }
         const int head = kvh * G + h0 + row;
         if (nsplit == 1) {
+            if (terms.sink) L += exp2f(__ldg(terms.sink + head) * LOG2E - M);
             out[(size_t)n * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
         } else if (CLUSTER) {
             part_o[row * D + d] = o;
@@ -481,6 +498,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
                 L += ml[1] * f;
                 o += *cluster.map_shared_rank(part_o + row * D + d, i) * f;
             }
+            if (terms.sink) L += exp2f(__ldg(terms.sink + kvh * G + h0 + row) * LOG2E - M);
             out[(size_t)n * out_stride + (size_t)(kvh * G + h0 + row) * D + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
         }
         cluster.sync();          // nobody leaves while a neighbour may still read its shared memory
@@ -535,6 +553,7 @@ attn_decode_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restric
         const float4* po = reinterpret_cast<const float4*>(partial_o + (group_base + (size_t)row * nsplit) * D) + d4;
         float L = 0.f;
         for (int i = 0; i < nsplit; ++i) L += lsum[row * nsplit + i];
+        if (terms.sink) L += exp2f(__ldg(terms.sink + kvh * G + h0 + row) * LOG2E - s_row_max[row]);
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         int i = 0;
         for (; i + 8 <= nsplit; i += 8) {          // fixed order of the sums: slice 0, 1, 2, ...
@@ -571,15 +590,19 @@ constexpr int PF_STAGE = 2 * PF_BN * DP;                      // K then V
 constexpr int PF_Q_ELEMS = PF_BM * DP;
 constexpr int PF_SMEM = PF_Q_ELEMS * 2 + 2 * PF_STAGE * 2 + 2 * PF_BN * 8;
 
+// TERMS: the softmax has a distance table, a sink, or values that are the keys (then v_cache == k_cache, a tile is
+// copied once and both products read it).
+template <bool TERMS>
 __global__ void __launch_bounds__(PF_WARPS * 32, (D <= 128 ? 2 : 1))
 attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restrict__ q, int q_stride,
                     const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                     const int* __restrict__ seq_kv_len, const int* __restrict__ seq_slot,
                     const int* __restrict__ block_table, int table_stride, const bf16* __restrict__ k_cache,
                     const bf16* __restrict__ v_cache, int Hq, int Hkv, int page_size, int num_pages, int window,
-                    float scale_log2e, int skip_single, int* status) {
+                    float scale_log2e, int skip_single, int* status, const ScoreTerms terms) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     TW_TIMELINE_SCOPE(TW_K_ATTN_PREFILL);
+    const bool values_are_keys = TERMS && v_cache == k_cache;
     tw_grid_wait();
     TW_TIMELINE_MARK();
     tw_grid_launch_dependents();
@@ -626,6 +649,15 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
             rlo[mt][h] = (window > 0 && rpos[mt][h] - window + 1 > 0) ? rpos[mt][h] - window + 1 : 0;
         }
     }
+    const float* brow[TERMS ? PF_MT : 1][2];        // the distance table's row of each of this thread's heads
+    if constexpr (TERMS) {
+#pragma unroll
+        for (int mt = 0; mt < PF_MT; ++mt) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                brow[mt][h] = terms.bias ? terms.bias + (size_t)(kvh * G + (wbase + 16 * mt + g + 8 * h) % G) * terms.reach : nullptr;
+        }
+    }
     float oacc[PF_MT][NT_O][4];
     float mrow[PF_MT][2], lrow[PF_MT][2];
 #pragma unroll
@@ -663,7 +695,7 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
             const int bytes = off >= 0 ? 16 : 0;
             const long long src = off >= 0 ? off + col * 8 : 0;
             cp_async16(ks_ + row * DP + col * 8, k_cache + src, bytes);
-            cp_async16(vs_ + row * DP + col * 8, v_cache + src, bytes);
+            if (!values_are_keys) cp_async16(vs_ + row * DP + col * 8, v_cache + src, bytes);
         }
         cp_async_commit();
     };
@@ -682,7 +714,7 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
         const int kb = key_begin + t * PF_BN;
         if (wbase < rows_total && kb <= warp_hi && kb + PF_BN > warp_lo) {
             const bf16* ks_ = stages + st * PF_STAGE;
-            const bf16* vs_ = ks_ + PF_BN * DP;
+            const bf16* vs_ = values_are_keys ? ks_ : ks_ + PF_BN * DP;
             float sacc[PF_MT][PF_BN / 8][4];
 #pragma unroll
             for (int mt = 0; mt < PF_MT; ++mt)
@@ -718,6 +750,12 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
                         const bool okb = rvalid[mt][1] && key <= rpos[mt][1] && key >= rlo[mt][1];
                         sacc[mt][nt][e] = oka ? sacc[mt][nt][e] * scale_log2e : NEG_INF;
                         sacc[mt][nt][2 + e] = okb ? sacc[mt][nt][2 + e] * scale_log2e : NEG_INF;
+                        if constexpr (TERMS) {
+                            if (terms.bias) {
+                                if (oka) sacc[mt][nt][e] = fmaf(__ldg(brow[mt][0] + min(rpos[mt][0] - key, terms.reach - 1)), LOG2E, sacc[mt][nt][e]);
+                                if (okb) sacc[mt][nt][2 + e] = fmaf(__ldg(brow[mt][1] + min(rpos[mt][1] - key, terms.reach - 1)), LOG2E, sacc[mt][nt][2 + e]);
+                            }
+                        }
                         rmax0 = fmaxf(rmax0, sacc[mt][nt][e]);
                         rmax1 = fmaxf(rmax1, sacc[mt][nt][2 + e]);
                     }
@@ -778,9 +816,15 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
         l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-        const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
         const int ra = wbase + 16 * mt + g, rb = ra + 8;
         const int ta = ra / G, tb = rb / G;
+        if constexpr (TERMS) {
+            if (terms.sink) {
+                l0 += exp2f(__ldg(terms.sink + kvh * G + ra - ta * G) * LOG2E - mrow[mt][0]);
+                l1 += exp2f(__ldg(terms.sink + kvh * G + rb - tb * G) * LOG2E - mrow[mt][1]);
+            }
+        }
+        const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
         bf16* oa = out + (size_t)(n0 + ta) * out_stride + (size_t)(kvh * G + ra - ta * G) * D;
         bf16* ob = out + (size_t)(n0 + tb) * out_stride + (size_t)(kvh * G + rb - tb * G) * D;
 #pragma unroll
@@ -808,7 +852,9 @@ int set_attrs() {
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_decode_kernel<true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+    e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
     if (e != cudaSuccess) return (int)e;
     g_attrs_set = true;
     return 0;
@@ -875,12 +921,13 @@ static int decode_refuses(int nsplit, const void* q, int q_stride) {
     return 0;
 }
 
-TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
-                             const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
-                             int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int Hq, int Hkv,
-                             int page_size, int num_pages, int window, float scale, int nsplit, int flags,
-                             float* scratch, int* counters, int* status, cudaStream_t stream) {
+static int decode_launch(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
+                         const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
+                         int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int Hq, int Hkv,
+                         int page_size, int num_pages, int window, float scale, int nsplit, int flags,
+                         float* scratch, int* counters, int* status, const ScoreTerms terms, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
+    if (terms.bias && terms.reach < 1) return (int)cudaErrorInvalidValue;
     if (Hkv <= 0 || Hq % Hkv || nsplit < 1 || (nsplit > 1 && (!scratch || !counters))) return (int)cudaErrorInvalidValue;
     if (int r = decode_refuses(nsplit, q, q_stride)) return r;
     // the merge reads the partial results 16 bytes at a time and writes 8 bytes of the result at a time
@@ -894,12 +941,35 @@ TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_str
         return tw_launch(attn_decode_kernel<true, false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, nsplit,
             (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
             table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{});
+            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{}, terms);
     tw_launch(attn_decode_kernel<false, false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{});
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{}, terms);
     return TW_LAUNCH_CHECK();
+}
+
+TW_EXPORT int tw_attn_decode(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
+                             const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
+                             int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int Hq, int Hkv,
+                             int page_size, int num_pages, int window, float scale, int nsplit, int flags,
+                             float* scratch, int* counters, int* status, cudaStream_t stream) {
+    return decode_launch(out, out_stride, q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, table_stride,
+                         k_cache, v_cache, n_seqs, Hq, Hkv, page_size, num_pages, window, scale, nsplit, flags, scratch,
+                         counters, status, ScoreTerms{}, stream);
+}
+
+// With a distance table (fp32 [Hq][reach], or null), a sink (fp32 [Hq], or null), and, when v_cache is k_cache,
+// values that are the keys.
+TW_EXPORT int tw_attn_decode_terms(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
+                                   const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
+                                   int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int Hq, int Hkv,
+                                   int page_size, int num_pages, int window, float scale, int nsplit, int flags,
+                                   float* scratch, int* counters, const float* bias, int reach, const float* sink,
+                                   int* status, cudaStream_t stream) {
+    return decode_launch(out, out_stride, q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, table_stride,
+                         k_cache, v_cache, n_seqs, Hq, Hkv, page_size, num_pages, window, scale, nsplit, flags, scratch,
+                         counters, status, ScoreTerms{bias, reach, sink}, stream);
 }
 
 // The same for a decode-only step whose q/k/v product has not been touched yet: the kernel adds the bias,
@@ -936,28 +1006,30 @@ TW_EXPORT int tw_attn_decode_fused(void* out, int out_stride, const float* parti
         return tw_launch(attn_decode_kernel<true, true>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, nsplit,
             (bf16*)out, out_stride, (const bf16*)nullptr, 0, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
             table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, fq);
+            scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, fq, ScoreTerms{});
     tw_launch(attn_decode_kernel<false, true>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1,
         (bf16*)out, out_stride, (const bf16*)nullptr, 0, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, fq);
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, fq, ScoreTerms{});
     return TW_LAUNCH_CHECK();
 }
 
+// bias, reach, sink: see ScoreTerms; all null and v_cache apart from k_cache: the plain softmax.
 TW_EXPORT int tw_attn_prefill(void* out, int out_stride, const void* q, int q_stride, const int* seq_q_start,
                               const int* seq_q_len, const int* seq_kv_len, const int* seq_slot, const int* block_table,
                               int table_stride, const void* k_cache, const void* v_cache, int n_seqs, int max_q_len,
                               int Hq, int Hkv, int page_size, int num_pages, int window, float scale, int skip_single,
-                              int* status, cudaStream_t stream) {
+                              const float* bias, int reach, const float* sink, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
-    if (Hkv <= 0 || Hq % Hkv) return (int)cudaErrorInvalidValue;
+    if (Hkv <= 0 || Hq % Hkv || (bias && reach < 1)) return (int)cudaErrorInvalidValue;
     if (int e = set_attrs()) return e;
     const int G = Hq / Hkv;
     dim3 grid((max_q_len * G + PF_BM - 1) / PF_BM, Hkv, n_seqs);
-    tw_launch(attn_prefill_kernel, dim3(grid), dim3(PF_WARPS * 32), PF_SMEM, stream, 1, 
-        (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
+    const bool with_terms = bias || sink || v_cache == k_cache;
+    tw_launch(with_terms ? attn_prefill_kernel<true> : attn_prefill_kernel<false>, dim3(grid), dim3(PF_WARPS * 32), PF_SMEM,
+        stream, 1, (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-        scale * 1.4426950408889634f, skip_single, status);
+        scale * 1.4426950408889634f, skip_single, status, ScoreTerms{bias, reach, sink});
     return TW_LAUNCH_CHECK();
 }
 
@@ -1035,6 +1107,6 @@ TW_EXPORT int tw_attn_decode_static(void* out, int out_stride, const void* q, in
     tw_launch(attn_decode_kernel<false, false>, dim3(grid), dim3(DEC_WARPS * 32), DEC_SMEM, stream, 1, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
         table_stride, (const bf16*)k_cache, (const bf16*)v_cache, Hq, Hkv, page_size, num_pages, window,
-        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{});
+        scale * 1.4426950408889634f, nsplit, partial_o, partial_ml, counters, status, FusedQkv{}, ScoreTerms{});
     return TW_LAUNCH_CHECK();
 }

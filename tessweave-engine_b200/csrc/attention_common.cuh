@@ -70,6 +70,16 @@ struct FusedQkv {
     long long next_bytes;
 };
 
+// What a softmax may have beside the scaled dot products; every member optional (null = absent).
+//   bias: fp32 [Hq][reach]; entry min(position - key position, reach - 1) of head h is added to h's scaled score.
+//   sink: fp32 [Hq]; exp(sink[h]) joins head h's denominator once (no key, no value, not scaled, no bias).
+struct ScoreTerms {
+    const float* bias;
+    int reach;
+    const float* sink;
+};
+constexpr float LOG2E = 1.4426950408889634f;
+
 // fp32 values of NC columns of one row of the q/k/v product, bias included.  The slices of a split product are
 // summed (0 + 4 + 8 ..), (1 + 5 + ..), .. first and then ((.) + (.)) + ((.) + (.)), as the kernel that otherwise
 // does this work sums them; the loads of all columns and of four slices are independent of one another.

@@ -1052,14 +1052,40 @@ TW_EXPORT int tw_add_delta(float* resid, const void* delta, const float* partial
 // acc[n] = (first ? 0 : acc[n]) + scale * x[n] / sqrt(mean(x[n]^2) + eps) * weight, row by row in fp32; `out` (may be
 // null) receives the new acc in the activation type.  For mixers that normalise each member's result before the sum.
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(256)
+template <typename T, bool ONE_PASS>
+__global__ void __launch_bounds__(TW_NORM_THREADS)
 normed_accumulate_kernel(float* __restrict__ acc, T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ weight,
                          float eps, float scale, int first, int width) {
     __shared__ float scratch[33];
     tw_grid_wait();
     tw_grid_launch_dependents();
     const size_t base = (size_t)blockIdx.x * width;
+    if (ONE_PASS) {
+        // the row, the old sum and the weight are all asked for before the first of them is needed
+        float v[TW_NORM_MAXV], a[TW_NORM_MAXV], wt[TW_NORM_MAXV];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < TW_NORM_MAXV; ++j) {
+            const int c = threadIdx.x + j * TW_NORM_THREADS;
+            const bool in = c < width;
+            v[j] = in ? tw_to_float(x[base + c]) : 0.f;
+            a[j] = (in && !first) ? acc[base + c] : 0.f;
+            wt[j] = in ? weight[c] : 0.f;
+            ss += v[j] * v[j];
+        }
+        ss = tw_block_sum(ss, scratch);
+        const float f = scale / sqrtf(ss / (float)width + eps);
+#pragma unroll
+        for (int j = 0; j < TW_NORM_MAXV; ++j) {
+            const int c = threadIdx.x + j * TW_NORM_THREADS;
+            if (c < width) {
+                const float r = a[j] + v[j] * f * wt[j];
+                acc[base + c] = r;
+                if (out) out[base + c] = tw_from_float<T>(r);
+            }
+        }
+        return;
+    }
     float ss = 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const float v = tw_to_float(x[base + c]);
@@ -1077,9 +1103,11 @@ normed_accumulate_kernel(float* __restrict__ acc, T* __restrict__ out, const T* 
 TW_EXPORT int tw_normed_accumulate(float* acc, void* out, const void* x, const float* weight, float eps, float scale, int first,
                                    int n_rows, int width, int dtype, cudaStream_t stream) {
     if (n_rows <= 0 || width <= 0) return 0;
+    const bool one = width <= TW_NORM_THREADS * TW_NORM_MAXV;
     if (dtype == TW_F32)
-        return tw_launch(normed_accumulate_kernel<float>, dim3(n_rows), dim3(256), 0, stream, 1, acc, (float*)out, (const float*)x,
-                         weight, eps, scale, first, width);
-    return tw_launch(normed_accumulate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, 1, acc, (__nv_bfloat16*)out,
-                     (const __nv_bfloat16*)x, weight, eps, scale, first, width);
+        return tw_launch(one ? normed_accumulate_kernel<float, true> : normed_accumulate_kernel<float, false>, dim3(n_rows),
+                         dim3(TW_NORM_THREADS), 0, stream, 1, acc, (float*)out, (const float*)x, weight, eps, scale, first, width);
+    return tw_launch(one ? normed_accumulate_kernel<__nv_bfloat16, true> : normed_accumulate_kernel<__nv_bfloat16, false>,
+                     dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, acc, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, weight,
+                     eps, scale, first, width);
 }

@@ -645,15 +645,28 @@ def _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_h
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: bad block table")
 
 
+def _score_terms_checks(sink, bias_rows, n_q_heads):
+    _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == n_q_heads and sink.is_contiguous()),
+          "attention: the sink must be fp32 [Hq]")
+    _need(bias_rows is None or (bias_rows.dtype == torch.float32 and bias_rows.dim() == 2 and bias_rows.shape[0] == n_q_heads
+                                and bias_rows.shape[1] > 0 and bias_rows.is_contiguous()),
+          "attention: the distance bias of the tensor-core kernels must be fp32 [Hq, distances]")
+
+
 def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,
                      n_q_heads, n_kv_heads, head_dim, window, scale, nsplit, scratch, counters, status,
-                     merge_in_scratch: bool = False) -> None:
+                     merge_in_scratch: bool = False, sink: torch.Tensor | None = None,
+                     bias_rows: torch.Tensor | None = None) -> None:
     """Split-KV attention for the requests of the batch that bring one token (others are skipped).
     Up to 16 slices merge inside a thread-block cluster; more (or all, with ``merge_in_scratch``)
     merge through ``scratch`` (fp32, the slices' partial results) and ``counters`` (int32, all
-    zero, left zero), which find the block that finishes last."""
-    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, counters, status)
+    zero, left zero), which find the block that finishes last.  ``sink`` fp32 [Hq]: exp(sink[h]) joins the
+    denominator of head h.  ``bias_rows`` fp32 [Hq, distances]: entry min(position - key position, distances - 1)
+    of head h is added to its scaled score.  ``v_pages`` may be ``k_pages`` (values that are the keys)."""
+    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, scratch, counters, status,
+          sink, bias_rows)
     _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    _score_terms_checks(sink, bias_rows, n_q_heads)
     _need(out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0, "attention_decode: output rows must be 8-byte aligned")
     _need(q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0, "attention_decode: rows of q must be 16-byte aligned")
     _need(1 <= nsplit <= DECODE_MAX_SPLITS, f"attention_decode: 1 to {DECODE_MAX_SPLITS} slices, not {nsplit}")
@@ -663,12 +676,15 @@ def attention_decode(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block
         _need(counters is not None and counters.dtype == torch.int32
               and counters.numel() >= n_seqs * n_kv_heads * ((n_q_heads // n_kv_heads + 7) // 8),
               "attention_decode: too few counters")
-    code = _fn("attention_bf16", "tw_attn_decode", {"TW_HEAD_DIM": head_dim})(
-        _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
-        _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
-        c_int(n_seqs), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
-        c_int(window), c_float(scale), c_int(nsplit), c_int(1 if merge_in_scratch else 0), _ptr(scratch), _ptr(counters),
-        _ptr(status), _stream())
+    head = (_ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
+            _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
+            c_int(n_seqs), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
+            c_int(window), c_float(scale), c_int(nsplit), c_int(1 if merge_in_scratch else 0), _ptr(scratch), _ptr(counters))
+    if sink is None and bias_rows is None:
+        code = _fn("attention_bf16", "tw_attn_decode", {"TW_HEAD_DIM": head_dim})(*head, _ptr(status), _stream())
+    else:
+        code = _fn("attention_bf16", "tw_attn_decode_terms", {"TW_HEAD_DIM": head_dim})(
+            *head, _ptr(bias_rows), c_int(0 if bias_rows is None else bias_rows.shape[1]), _ptr(sink), _ptr(status), _stream())
     _check(code, "attention_decode")
 
 
@@ -937,15 +953,19 @@ def attention_prefill_tcgen05(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_sl
 
 
 def attention_prefill(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, n_seqs,
-                      max_q_len, n_q_heads, n_kv_heads, head_dim, window, scale, skip_single, status) -> None:
-    """Flash attention over the paged cache for the requests that bring several tokens."""
-    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, status)
+                      max_q_len, n_q_heads, n_kv_heads, head_dim, window, scale, skip_single, status,
+                      sink: torch.Tensor | None = None, bias_rows: torch.Tensor | None = None) -> None:
+    """Flash attention over the paged cache for the requests that bring several tokens.  ``sink``, ``bias_rows`` and
+    ``v_pages`` that are ``k_pages``: as for ``attention_decode``."""
+    _cuda(out, q, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages, v_pages, status, sink, bias_rows)
     _attn_common_checks(out, q, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    _score_terms_checks(sink, bias_rows, n_q_heads)
     code = _fn("attention_bf16", "tw_attn_prefill", {"TW_HEAD_DIM": head_dim})(
         _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len),
         _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages),
         c_int(n_seqs), c_int(max_q_len), c_int(n_q_heads), c_int(n_kv_heads), c_int(k_pages.shape[2]),
-        c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(1 if skip_single else 0), _ptr(status), _stream())
+        c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(1 if skip_single else 0), _ptr(bias_rows),
+        c_int(0 if bias_rows is None else bias_rows.shape[1]), _ptr(sink), _ptr(status), _stream())
     _check(code, "attention_prefill")
 
 
@@ -1529,13 +1549,17 @@ SHORT_CONV_MAX_TAPS = 17
 
 def short_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, state_offset: int,
                seq_of_token: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor, n_rows: int,
-               unit_heads: int = 0, unit_dim: int = 0, scaled_heads: int = 0, head_scale: float = 1.0, unit_eps: float = 0.0) -> None:
+               unit_heads: int = 0, unit_dim: int = 0, scaled_heads: int = 0, head_scale: float = 1.0, unit_eps: float = 0.0,
+               move_single: torch.Tensor | None = None) -> None:
     """out[t, c] = silu(sum_j w[c, j] x[t - (taps - 1) + j, c]) in fp32 [rows, channels]: a causal convolution over the
     rows of each request, per channel (the last tap is the row's own).  The taps - 1 rows before a request's first row of
     this step are read from its state (fp32, [channels, taps - 1] at ``state_offset``; zeros at a request's start).  The
     first ``unit_heads`` heads of ``unit_dim`` channels are then scaled to x / sqrt(sum x^2 + unit_eps), the first
-    ``scaled_heads`` of those also by ``head_scale``.  ``short_conv_state`` moves the state on afterwards."""
-    _cuda(out, x, w, state, seq_of_token, seq_slot, seq_q_start)
+    ``scaled_heads`` of those also by ``head_scale``.  ``short_conv_state`` moves the state on afterwards; with
+    ``move_single`` (the requests' row counts of this step, int32) the kernel itself moves on the state of every request
+    that brings one row, and ``short_conv_state(..., skip_single=True)`` is needed only for the others."""
+    _cuda(out, x, w, state, seq_of_token, seq_slot, seq_q_start, move_single)
+    _need(move_single is None or move_single.dtype == torch.int32, "short_conv: the row counts must be int32")
     channels, taps = w.shape
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == channels and out.shape[0] >= n_rows,
           "short_conv: the result must be contiguous fp32 [rows, channels]")
@@ -1546,20 +1570,22 @@ def short_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, state: torch
     _need(0 <= scaled_heads <= unit_heads and unit_heads * unit_dim <= channels, "short_conv: the unit heads exceed the channels")
     code = _fn("recurrent", "tw_short_conv")(
         _ptr(out), _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(taps), _ptr(state), ctypes.c_longlong(state.stride(0)),
-        ctypes.c_longlong(state_offset), _ptr(seq_of_token), _ptr(seq_slot), _ptr(seq_q_start), c_int(n_rows), c_int(channels),
+        ctypes.c_longlong(state_offset), _ptr(seq_of_token), _ptr(seq_slot), _ptr(seq_q_start), _ptr(move_single),
+        c_int(0 if move_single is None else 1), c_int(n_rows), c_int(channels),
         c_int(unit_heads), c_int(unit_dim), c_int(scaled_heads), c_float(head_scale), c_float(unit_eps), c_int(dtype_code(x.dtype)), _stream())
     _check(code, "short_conv")
 
 
 def short_conv_state(x: torch.Tensor, taps: int, channels: int, state: torch.Tensor, state_offset: int, seq_slot: torch.Tensor,
-                     seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int) -> None:
+                     seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int, skip_single: bool = False) -> None:
     """After ``short_conv``: every request's state keeps the last ``taps - 1`` inputs (older ones stay where the step
-    brought fewer rows than that)."""
+    brought fewer rows than that).  ``skip_single``: requests with one row are left as they are."""
     _cuda(x, state, seq_slot, seq_q_start, seq_q_len)
     _need(x.stride(1) == 1 and x.shape[1] >= channels and 1 <= taps <= SHORT_CONV_MAX_TAPS, "short_conv_state: bad input rows or taps")
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
           and state_offset + channels * (taps - 1) <= state.shape[1], "short_conv_state: the state must be fp32 [slots, numel] with room for the taps")
     code = _fn("recurrent", "tw_short_conv_state")(
         _ptr(x), c_int(x.stride(0)), c_int(taps), _ptr(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(state_offset),
-        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(channels), c_int(dtype_code(x.dtype)), _stream())
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(channels), c_int(1 if skip_single else 0),
+        c_int(dtype_code(x.dtype)), _stream())
     _check(code, "short_conv_state")

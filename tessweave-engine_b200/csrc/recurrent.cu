@@ -341,39 +341,50 @@ TW_EXPORT int tw_tanh_rows(void* x, long long count, int dtype, cudaStream_t str
 template <typename T>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(float* __restrict__ out, const T* __restrict__ x, int x_stride, const float* __restrict__ w, int taps,
-                  const float* __restrict__ state, long long state_stride, long long state_offset,
+                  float* __restrict__ state, long long state_stride, long long state_offset,
                   const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
-                  int channels, int unit_heads, int unit_dim, int scaled_heads, float head_scale, float unit_eps) {
-    extern __shared__ float sy[];        // [channels]
+                  const int* __restrict__ seq_q_len, int move_single, int channels, int chunk, int unit_heads, int unit_dim,
+                  int scaled_heads, float head_scale, float unit_eps) {
+    extern __shared__ float sy[];        // [chunk]
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int row = blockIdx.x;
     const int s = seq_of_token[row];
     if (s < 0) return;
+    // this block's channels: a whole number of unit heads, so that no head's sum of squares crosses blocks
+    const int c0 = blockIdx.y * chunk, c1 = min(channels, c0 + chunk);
     const int r = row - seq_q_start[s];                  // rows of this request before this one in the step
-    const float* tail = state + (size_t)seq_slot[s] * state_stride + state_offset;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    float* tail = state + (size_t)seq_slot[s] * state_stride + state_offset;
+    // A request that brings one row has no other block that reads these channels of its state: the thread that read
+    // them moves them on itself (the oldest input leaves, the row's own joins), and the step needs no second kernel.
+    const bool move = move_single && seq_q_len[s] == 1 && taps > 1;
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
         float acc = 0.f;
+        float* tc = tail + (size_t)c * (taps - 1);
         for (int j = 0; j < taps; ++j) {
             const int back = taps - 1 - j;               // how many rows before this one
-            const float xv = back <= r ? tw_to_float(x[(size_t)(row - back) * x_stride + c])
-                                       : tail[(size_t)c * (taps - 1) + (taps - 1 + r - back)];
+            const float xv = back <= r ? tw_to_float(x[(size_t)(row - back) * x_stride + c]) : tc[taps - 1 + r - back];
             acc += w[(size_t)c * taps + j] * xv;
+            if (move && j > 0) tc[j - 1] = xv;           // r == 0: xv is input j of (state, own row); place j - 1 has been read
         }
-        sy[c] = acc / (1.0f + expf(-acc));
+        sy[c - c0] = acc / (1.0f + expf(-acc));
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     float* orow = out + (size_t)row * channels;
-    for (int head = warp; head < unit_heads; head += nwarps) {
-        const float* y = sy + head * unit_dim;
-        float ss = 0.f;
-        for (int d = lane; d < unit_dim; d += 32) ss += y[d] * y[d];
-        ss = tw_warp_sum(ss);
-        const float f = (head < scaled_heads ? head_scale : 1.0f) / sqrtf(ss + unit_eps);
-        for (int d = lane; d < unit_dim; d += 32) orow[head * unit_dim + d] = y[d] * f;
+    const int unit_end = unit_heads * unit_dim;
+    if (c0 < unit_end) {
+        const int h0 = c0 / unit_dim, h1 = min(unit_heads, (c1 + unit_dim - 1) / unit_dim);
+        for (int head = h0 + warp; head < h1; head += nwarps) {
+            const float* y = sy + (head * unit_dim - c0);
+            float ss = 0.f;
+            for (int d = lane; d < unit_dim; d += 32) ss += y[d] * y[d];
+            ss = tw_warp_sum(ss);
+            const float f = (head < scaled_heads ? head_scale : 1.0f) / sqrtf(ss + unit_eps);
+            for (int d = lane; d < unit_dim; d += 32) orow[head * unit_dim + d] = y[d] * f;
+        }
     }
-    for (int c = unit_heads * unit_dim + threadIdx.x; c < channels; c += blockDim.x) orow[c] = sy[c];
+    for (int c = max(c0, unit_end) + threadIdx.x; c < c1; c += blockDim.x) orow[c] = sy[c - c0];
 }
 
 // The convolution's state after the step: the last taps - 1 inputs of every request, older ones kept where the
@@ -381,13 +392,14 @@ short_conv_kernel(float* __restrict__ out, const T* __restrict__ x, int x_stride
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ x, int x_stride, int taps, float* __restrict__ state,
                                         long long state_stride, long long state_offset, const int* __restrict__ seq_slot,
-                                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len, int channels) {
+                                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len, int channels,
+                                        int skip_single) {
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int s = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int len = seq_q_len[s];
-    if (c >= channels || len <= 0) return;
+    if (c >= channels || len <= 0 || (skip_single && len == 1)) return;     // (tw_short_conv has moved the single rows' state on)
     const int start = seq_q_start[s], keep = taps - 1;
     float* tail = state + (size_t)seq_slot[s] * state_stride + state_offset + (size_t)c * keep;
     float fresh[16];
@@ -398,40 +410,52 @@ __global__ void short_conv_state_kernel(const T* __restrict__ x, int x_stride, i
     for (int j = 0; j < keep; ++j) tail[j] = fresh[j];
 }
 
-TW_EXPORT int tw_short_conv(float* out, const void* x, int x_stride, const float* w, int taps, float* state,
-                            long long state_stride, long long state_offset, const int* seq_of_token, const int* seq_slot,
-                            const int* seq_q_start, int n_rows, int channels, int unit_heads, int unit_dim, int scaled_heads,
-                            float head_scale, float unit_eps, int dtype, cudaStream_t stream) {
-    if (n_rows <= 0 || channels <= 0) return 0;
-    if (taps < 1 || taps > 17 || unit_heads * unit_dim > channels) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)channels * sizeof(float);
-    if (dtype == TW_F32) {
-        if (smem > 48 * 1024) {
-            const cudaError_t e = cudaFuncSetAttribute(short_conv_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        return tw_launch(short_conv_kernel<float>, dim3(n_rows), dim3(256), smem, stream, 1, out, (const float*)x, x_stride, w, taps,
-                         (const float*)state, state_stride, state_offset, seq_of_token, seq_slot, seq_q_start, channels,
-                         unit_heads, unit_dim, scaled_heads, head_scale, unit_eps);
-    }
+template <typename T>
+static int launch_short_conv(float* out, const T* x, int x_stride, const float* w, int taps, float* state, long long state_stride,
+                             long long state_offset, const int* seq_of_token, const int* seq_slot, const int* seq_q_start,
+                             const int* seq_q_len, int move_single, int n_rows, int channels, int unit_heads, int unit_dim,
+                             int scaled_heads, float head_scale, float unit_eps, cudaStream_t stream) {
+    // about 512 channels per block, in whole unit heads while there are any (a head larger than that has a block of its own)
+    int chunk = 512;
+    if (unit_heads > 0 && unit_dim > 0) chunk = unit_dim * (unit_dim >= 512 ? 1 : 512 / unit_dim);
+    const size_t smem = (size_t)chunk * sizeof(float);
     if (smem > 48 * 1024) {
-        const cudaError_t e = cudaFuncSetAttribute(short_conv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(short_conv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return tw_launch(short_conv_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), smem, stream, 1, out, (const __nv_bfloat16*)x,
-                     x_stride, w, taps, (const float*)state, state_stride, state_offset, seq_of_token, seq_slot, seq_q_start,
-                     channels, unit_heads, unit_dim, scaled_heads, head_scale, unit_eps);
+    const dim3 grid(n_rows, (channels + chunk - 1) / chunk);
+    return tw_launch(short_conv_kernel<T>, grid, dim3(256), smem, stream, 1, out, x, x_stride, w, taps, state, state_stride,
+                     state_offset, seq_of_token, seq_slot, seq_q_start, seq_q_len, move_single, channels, chunk, unit_heads,
+                     unit_dim, scaled_heads, head_scale, unit_eps);
+}
+
+// seq_q_len with move_single: requests that bring one row have their state moved on by this kernel (and
+// tw_short_conv_state is then told to skip them).
+TW_EXPORT int tw_short_conv(float* out, const void* x, int x_stride, const float* w, int taps, float* state,
+                            long long state_stride, long long state_offset, const int* seq_of_token, const int* seq_slot,
+                            const int* seq_q_start, const int* seq_q_len, int move_single, int n_rows, int channels,
+                            int unit_heads, int unit_dim, int scaled_heads, float head_scale, float unit_eps, int dtype,
+                            cudaStream_t stream) {
+    if (n_rows <= 0 || channels <= 0) return 0;
+    if (taps < 1 || taps > 17 || unit_heads * unit_dim > channels || (move_single && !seq_q_len)) return (int)cudaErrorInvalidValue;
+    if (dtype == TW_F32)
+        return launch_short_conv<float>(out, (const float*)x, x_stride, w, taps, state, state_stride, state_offset, seq_of_token,
+                                        seq_slot, seq_q_start, seq_q_len, move_single, n_rows, channels, unit_heads, unit_dim,
+                                        scaled_heads, head_scale, unit_eps, stream);
+    return launch_short_conv<__nv_bfloat16>(out, (const __nv_bfloat16*)x, x_stride, w, taps, state, state_stride, state_offset,
+                                            seq_of_token, seq_slot, seq_q_start, seq_q_len, move_single, n_rows, channels,
+                                            unit_heads, unit_dim, scaled_heads, head_scale, unit_eps, stream);
 }
 
 TW_EXPORT int tw_short_conv_state(const void* x, int x_stride, int taps, float* state, long long state_stride,
                                   long long state_offset, const int* seq_slot, const int* seq_q_start, const int* seq_q_len,
-                                  int n_seqs, int channels, int dtype, cudaStream_t stream) {
+                                  int n_seqs, int channels, int skip_single, int dtype, cudaStream_t stream) {
     if (n_seqs <= 0 || channels <= 0 || taps <= 1) return 0;
     if (taps > 17) return (int)cudaErrorInvalidValue;
     const dim3 grid((channels + 127) / 128, n_seqs);
     if (dtype == TW_F32)
         return tw_launch(short_conv_state_kernel<float>, grid, dim3(128), 0, stream, 1, (const float*)x, x_stride, taps, state,
-                         state_stride, state_offset, seq_slot, seq_q_start, seq_q_len, channels);
+                         state_stride, state_offset, seq_slot, seq_q_start, seq_q_len, channels, skip_single);
     return tw_launch(short_conv_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, (const __nv_bfloat16*)x, x_stride, taps,
-                     state, state_stride, state_offset, seq_slot, seq_q_start, seq_q_len, channels);
+                     state, state_stride, state_offset, seq_slot, seq_q_start, seq_q_len, channels, skip_single);
 }

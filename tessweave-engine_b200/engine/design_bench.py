@@ -447,10 +447,11 @@ def nufatar_kernel_table(config: dict, batch: int, context: int, prefill_tokens:
                              torch.empty(m, H * Dv, device=dev), torch.randn(m, 2 * H, device=dev),
                              torch.randn(m, H * Dk, device=dev) if side.channel_decay else None))
             if label == "a decay per head":
-                def conv(s):
+                def conv(s):      # as the delta rule calls them: single rows move their state on in the convolution itself
                     ops.short_conv(s[1], s[0], conv_w, s[2], numel, seq_of, slots, starts, m, unit_heads=2 * Gq, unit_dim=Dk,
-                                   scaled_heads=Gq, head_scale=Dk ** -0.5, unit_eps=1e-6)
-                    ops.short_conv_state(s[0], taps, C, s[2], numel, slots, starts, lens, requests)
+                                   scaled_heads=Gq, head_scale=Dk ** -0.5, unit_eps=1e-6, move_single=lens)
+                    if per > 1:
+                        ops.short_conv_state(s[0], taps, C, s[2], numel, slots, starts, lens, requests, skip_single=True)
                 add(f"{phase}: convolutions of {taps} taps + silu + unit norms, {C} channels", m, [(lambda s=s: conv(s)) for s in sets],
                     m * C * 6 + 2 * requests * C * (taps - 1) * 4, 0.0, reps=8)
             for s in sets:

@@ -36,7 +36,10 @@ class GQAAttention(Mixer):
     ``distance_bias`` (``name``, ``rows``, ``far``): a learned table [rows, n_heads] added to the scaled score by
     bucketed distance n = position - key position: bucket(n) = n below rows // 2, else
     min(rows - 1, rows // 2 + floor(ln(n / (rows // 2)) / ln(far / (rows // 2)) * (rows - rows // 2))); the table by
-    plain distance is made once, when the weights are in.  A mixer with any of the three attends with the exact kernel.
+    plain distance is made once, when the weights are in.  A mixer with any of the three stores its keys with the
+    separate step and attends with the mma.sync kernels (prefill and split-KV decode), which add the table's entry to
+    each score and the sink to the denominator, and read a tile of keys once for both products; in 32-bit, and with
+    head sizes those kernels do not take, it attends with the exact kernel.
     """
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
@@ -83,8 +86,9 @@ class GQAAttention(Mixer):
                 raise ValueError(f"attention: a distance table needs at least 2 rows and a far distance beyond rows // 2, got {rows} and {far}")
             self.distance_bias = {"name": str(distance_bias["name"]), "rows": rows, "far": far}
             self.bias_table = runtime.empty(rows, n_heads, dtype=torch.float32)
-        # what only the exact kernel knows
-        self.exact_only = self.values_are_keys or self.sink is not None or self.distance_bias is not None
+        # terms of the softmax that the kernels fed by TMA and the kernels that rotate on the way do not know
+        self.score_terms = self.values_are_keys or self.sink is not None or self.distance_bias is not None
+        self.bias_rows = None
 
     @staticmethod
     def distance_bucket(n: int, rows: int, far: float) -> int:
@@ -103,6 +107,7 @@ class GQAAttention(Mixer):
             buckets = [self.distance_bucket(n, rows, far) for n in range(reach)]
             index = torch.tensor(buckets, dtype=torch.long, device=self.bias_table.device)
             self.bias_by_distance = self.bias_table.index_select(0, index).contiguous()
+            self.bias_rows = self.bias_by_distance.t().contiguous()        # [heads, distances]: a head's row is contiguous
 
     def weights(self) -> list[WeightDecl]:
         q, kv, nm = self.q_size, self.kv_size, self.names
@@ -125,7 +130,7 @@ class GQAAttention(Mixer):
 
     def _fused_table(self):
         """The rotation table of the kernels that rotate on the way; None where the mixer takes the separate steps."""
-        return self.position.fused_rotary_table(self.head_dim) if self.same_dims and not self.exact_only else None
+        return self.position.fused_rotary_table(self.head_dim) if self.same_dims and not self.score_terms else None
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
         if not isinstance(cache, PagedView):
@@ -158,7 +163,7 @@ class GQAAttention(Mixer):
     def _decode_launch(self, ctx: StepContext, cache: PagedView) -> tuple[bool, int, int]:
         """(fed by TMA?, slices per request, blocks) of the decode attention this step will launch."""
         group = self.n_heads // self.n_kv_heads
-        tma = ops.decode_tma_supported(self.runtime.dtype, self.head_dim, cache.page_size)
+        tma = not self.score_terms and ops.decode_tma_supported(self.runtime.dtype, self.head_dim, cache.page_size)
         splits = ops.decode_tma_splits if tma else ops.decode_splits
         nsplit = splits(ctx.n_seqs, self.n_kv_heads, group, ctx.max_kv_len)
         return tma, nsplit, ctx.n_seqs * self.n_kv_heads * -(-group // 8) * nsplit
@@ -196,7 +201,7 @@ class GQAAttention(Mixer):
             # decode-only step: the attention kernel adds the bias, rotates, writes the new key and value and attends
             self._decode(ctx, out, None, cache, fused=(source if source is not None else qkv, table, write_cache))
             return out
-        if not self.same_dims or self.exact_only:
+        if not self.same_dims or self.score_terms:
             # keys and values of different sizes, or what only the exact kernel knows: bias, the position part's own
             # transformation, then the store (values that are the keys share the keys' pages: one store)
             if self.b_qkv is not None:
@@ -233,11 +238,12 @@ class GQAAttention(Mixer):
             prefill = ops.attention_prefill
             # (not with a window: that kernel copies whole key tiles, and the pages of a tile's keys before the
             # earliest window may have been given back; the mma.sync kernel skips such keys one by one)
-            if not window and ops.prefer_tcgen05_attention(self.runtime.dtype, self.head_dim, cache.k_pages.shape[2], ctx.max_q_len):
+            if not window and not self.score_terms and ops.prefer_tcgen05_attention(self.runtime.dtype, self.head_dim, cache.k_pages.shape[2], ctx.max_q_len):
                 prefill = ops.attention_prefill_tcgen05
             prefill(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
                                   cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, ctx.max_q_len,
-                                  self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale, singles, ctx.status)
+                                  self.n_heads, self.n_kv_heads, self.head_dim, window, self.scale, singles, ctx.status,
+                                  **self._terms())
         if singles:
             self._decode(ctx, out, q, cache)
 
@@ -268,11 +274,14 @@ class GQAAttention(Mixer):
             ops.attention_decode(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
                                  cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, self.n_heads,
                                  self.n_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, counters,
-                                 ctx.status)
+                                 ctx.status, **self._terms())
+
+    def _terms(self) -> dict:
+        return {"sink": self.sink, "bias_rows": self.bias_rows} if self.score_terms else {}
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
         q = qkv[:, : self.q_size]
-        if self.same_dims and not self.exact_only and ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim):
+        if self.same_dims and ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim):
             self._attend_tensor_cores(ctx, out, q, cache)
             return
         ops.attention_generic(out, q, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table,

@@ -385,10 +385,12 @@ class GatedDelta(MatrixStateMixer):
         ready = ws.get("delta.ready", (n, C), torch.float32)
         ops.short_conv(ready, proj, self.conv, cache.state, self.conv_offset, ctx.seq_of_token, ctx.seq_slot, ctx.seq_q_start, n,
                        unit_heads=2 * self.n_qk_heads, unit_dim=self.key_dim, scaled_heads=self.n_qk_heads,
-                       head_scale=self.key_dim ** -0.5, unit_eps=self.UNIT_EPS)
-        if write_cache and self.taps > 1:
+                       head_scale=self.key_dim ** -0.5, unit_eps=self.UNIT_EPS,
+                       move_single=ctx.seq_q_len if write_cache else None)
+        if write_cache and self.taps > 1 and not ctx.decode_only:
+            # (a request that brings one row had its state moved on by the convolution itself)
             ops.short_conv_state(proj, self.taps, C, cache.state, self.conv_offset, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len,
-                                 ctx.n_seqs)
+                                 ctx.n_seqs, skip_single=True)
         raw, _ = self._recur(ctx, ready[:, :a], ready[:, a:2 * a], ready[:, 2 * a:], cache, write_cache, pre=decay,
                              p0=self.rate_log, p1=self.dt_bias, write_pre=small, channel_decay=self.channel_decay,
                              qk_group=H // self.n_qk_heads)

@@ -117,8 +117,10 @@ def paged_setup(lengths, page, kv_heads, head_dim, dtype, seed=0, extra_pages=5)
     return dict(table=dev(table), slots=slots, k_pages=dev(k_pages, dtype), v_pages=dev(v_pages, dtype), k=ks, v=vs)
 
 
-def dense_attention(q, k, v, positions, window=None):
-    """q: [rows, Hq, D] at the given positions of one request; k, v: [n, Hkv, D]; fp32."""
+def dense_attention(q, k, v, positions, window=None, sink=None, bias_rows=None):
+    """q: [rows, Hq, D] at the given positions of one request; k, v: [n, Hkv, D]; fp32.  ``sink`` [Hq]: a column of
+    its own in the softmax that carries no value.  ``bias_rows`` [Hq, distances]: added to the score by distance,
+    distances from the last entry on sharing it."""
     rep = q.shape[1] // k.shape[1]
     kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
     s = torch.einsum("rhd,nhd->hrn", q, kk) * q.shape[-1] ** -0.5
@@ -127,7 +129,13 @@ def dense_attention(q, k, v, positions, window=None):
     visible = p[None, :] <= pos[:, None]
     if window:
         visible &= p[None, :] > pos[:, None] - window
+    if bias_rows is not None:
+        dist = (pos[:, None] - p[None, :]).clamp(0, bias_rows.shape[1] - 1)
+        s = s + bias_rows[:, dist]
     s = s.masked_fill(~visible[None], float("-inf"))
+    if sink is not None:
+        s = torch.cat([s, sink[:, None, None].expand(-1, s.shape[1], 1)], -1)
+        return torch.einsum("hrn,nhd->rhd", torch.softmax(s, -1)[..., :-1], vv)
     return torch.einsum("hrn,nhd->rhd", torch.softmax(s, -1), vv)
 
 
@@ -306,7 +314,7 @@ TC_CASES = [(8, 8, 16), (8, 2, 32), (8, 1, 64), (6, 3, 48), (28, 4, 128), (4, 2,
 
 
 def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None, merge_in_scratch=False, tcgen05=False,
-                              tma=False, stages=0):
+                              tma=False, stages=0, **terms):
     """rows_of: request -> the consecutive positions it brings; the request holds exactly
     positions 0..last.  Requests with one row go through the decode kernel (with ``tma`` the one fed by TMA)."""
     o = ops()
@@ -323,7 +331,7 @@ def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None
     if any(len(r) > 1 for r in rows_of):
         prefill = o.attention_prefill_tcgen05 if tcgen05 else o.attention_prefill
         prefill(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
-                            len(rows_of), max(len(r) for r in rows_of), hq, hkv, d, window, d ** -0.5, singles, st)
+                            len(rows_of), max(len(r) for r in rows_of), hq, hkv, d, window, d ** -0.5, singles, st, **terms)
     if singles:
         max_kv = max(r[-1] + 1 for r in rows_of)
         ns = nsplit or o.decode_splits(len(rows_of), hkv, hq // hkv, max_kv)
@@ -338,7 +346,7 @@ def run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=None
             else:
                 o.attention_decode(out, qd, q_start, q_len, kv_len, slot, setup["table"], setup["k_pages"], setup["v_pages"],
                                    len(rows_of), hq, hkv, d, window, d ** -0.5, ns, scratch, counters, st,
-                                   merge_in_scratch=merge_in_scratch)
+                                   merge_in_scratch=merge_in_scratch, **terms)
         assert int(counters.abs().sum()) == 0
     assert int(st) == 0
     return out.float().cpu().reshape(n, hq, d), qd.float().cpu().reshape(n, hq, d)
@@ -363,6 +371,43 @@ def test_tensor_core_attention_mixed_rows(hq, hkv, d, window):
         want = dense_attention(qr[cursor:cursor + len(r)], k, v, r, window or None)
         assert torch.allclose(got[cursor:cursor + len(r)], want, **TOL["bfloat16"]), f"request {i}"
         cursor += len(r)
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(6, 3, 64), (28, 4, 128), (9, 1, 32), (8, 8, 16), (10, 2, 48)])
+@pytest.mark.parametrize("window,reach", [(0, 50), (40, 40), (100, 30)])
+@pytest.mark.parametrize("nsplit,merge_in_scratch", [(None, False), (1, False), (3, False), (5, True), (17, False)])
+def test_tensor_core_attention_with_sink_distance_table_and_keys_as_values(hq, hkv, d, window, reach, nsplit, merge_in_scratch):
+    """The mma.sync kernels with a sink in the denominator, a table of biases by distance (shorter than, as long as
+    and -- without a window -- far shorter than what a query sees) and the key pages given as the value pages: two
+    single rows beside two portions, every way of merging a single row's slices."""
+    lengths = [1, 300, 65, 257]
+    page = 16 if d != 48 else 8
+    setup = paged_setup(lengths, page, hkv, d, torch.bfloat16, seed=hq * 10 + d)
+    setup["v_pages"] = setup["k_pages"]
+    rows_of = [[0], [299], list(range(0, 65)), list(range(200, 257))]
+    g = torch.Generator().manual_seed(6)
+    n = sum(len(r) for r in rows_of)
+    q = torch.randn(n, hq, d, generator=g)
+    sink = torch.linspace(-1.0, 3.0, hq)
+    bias_rows = 2.0 * torch.randn(hq, reach, generator=g)
+    got, qr = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=nsplit, merge_in_scratch=merge_in_scratch,
+                                        sink=dev(sink), bias_rows=dev(bias_rows))
+    cursor = 0
+    for i, r in enumerate(rows_of):
+        k = setup["k"][i].to(torch.bfloat16).float()
+        want = dense_attention(qr[cursor:cursor + len(r)], k, k, r, window or None, sink=sink, bias_rows=bias_rows)
+        assert torch.allclose(got[cursor:cursor + len(r)], want, **TOL["bfloat16"]), f"request {i}"
+        cursor += len(r)
+    # each term alone: the sink without a table, the table without a sink, and neither over pages that are both
+    for terms in ({"sink": dev(sink)}, {"bias_rows": dev(bias_rows)}, {}):
+        got, _ = run_tensor_core_attention(setup, rows_of, q, hq, hkv, d, window, nsplit=nsplit, merge_in_scratch=merge_in_scratch, **terms)
+        cursor = 0
+        for i, r in enumerate(rows_of):
+            k = setup["k"][i].to(torch.bfloat16).float()
+            want = dense_attention(qr[cursor:cursor + len(r)], k, k, r, window or None, sink=sink if "sink" in terms else None,
+                                   bias_rows=bias_rows if "bias_rows" in terms else None)
+            assert torch.allclose(got[cursor:cursor + len(r)], want, **TOL["bfloat16"]), f"request {i} with {sorted(terms)}"
+            cursor += len(r)
 
 
 @pytest.mark.parametrize("tma", [False, True])
