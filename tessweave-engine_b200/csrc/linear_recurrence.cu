@@ -35,6 +35,8 @@
 // Threads that share a column of the state: each owns TW_DK / TW_REC_KSPLIT of its key channels (lanes l, l + 8,
 // l + 16, l + 24 of a warp), and their partial outputs are added by two shuffles.
 #define TW_REC_KSPLIT ((TW_DK % 16 == 0) ? 4 : 1)
+#define TW_REC_SEG (TW_DK / TW_REC_KSPLIT + (TW_REC_KSPLIT > 1 ? 4 : 0))
+#define TW_REC_DKP (TW_REC_SEG * TW_REC_KSPLIT)
 
 enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2, TW_REC_DELTA = 3 };
 
@@ -72,6 +74,10 @@ __global__ void __launch_bounds__(512)
 linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sm[];
     constexpr int DK = TW_DK, C = TW_REC_CHUNK, KS = TW_REC_KSPLIT, SK = DK / KS;
+    // A staged row keeps the KS shares of its key channels four floats apart (SEG = SK + 4), so that the four 16-byte
+    // reads a warp issues at once (one per share) fall into different banks; DKP is the padded row.
+    constexpr int SEG = TW_REC_SEG, DKP = TW_REC_DKP;
+    auto pad = [](int i) { return KS > 1 ? i + 4 * (i / SK) : i; };
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int h = blockIdx.x, s = blockIdx.y;
@@ -89,9 +95,9 @@ linear_recurrence_kernel(RecArgs a) {
     const bool live = walks && j < cols;
     // a staged chunk: q [C][DK], k [C][DK], w [C][DK] (wkv) or gates [C][2] (mlstm), v [C][per]; two of them, so that
     // the rows of the next 16 tokens are staged while the state walks through these
-    const int extra = MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : (MODE == TW_REC_DELTA ? C * DK + 2 * C : 0));
-    const int chunk_floats = 2 * C * DK + extra + C * per;
-    float* su = sm + 2 * chunk_floats;      // [DK] bonus (wkv)
+    const int extra = MODE == TW_REC_WKV ? C * DKP : (MODE == TW_REC_MLSTM ? 2 * C : (MODE == TW_REC_DELTA ? C * DKP + 2 * C : 0));
+    const int chunk_floats = 2 * C * DKP + extra + C * per;
+    float* su = sm + 2 * chunk_floats;      // [DKP] bonus (wkv)
     const long long head_state = (long long)DK * cols + (MODE == TW_REC_MLSTM ? 1 : 0);
     float* slot = a.state + (size_t)a.seq_slot[s] * a.state_stride + (size_t)h * head_state;
     const T* __restrict__ gq = (const T*)a.q;
@@ -99,13 +105,18 @@ linear_recurrence_kernel(RecArgs a) {
     const T* __restrict__ gv = (const T*)a.v;
     const int half = a.rot_dims >> 1;
     const int hq = h / a.qk_group;      // the head of q and k this head reads
+    const float rate = MODE == TW_REC_DELTA ? expf(a.p0[h]) : 0.f;     // delta: the head's decay rate
+    const bool vec_rows = MODE == TW_REC_DELTA && sizeof(T) == 4 && (a.q_stride % 4) == 0 && (a.k_stride % 4) == 0
+                          && (reinterpret_cast<size_t>(a.q) % 16) == 0 && (reinterpret_cast<size_t>(a.k) % 16) == 0
+                          && (!a.channel_decay || ((a.wpre_stride % 4) == 0 && (reinterpret_cast<size_t>(a.wpre) % 16) == 0
+                                                   && (reinterpret_cast<size_t>(a.p1) % 16) == 0));
 
     // ---- the rows of up to C tokens from t0 on, as fp32: rotation, scaling, decays and gates are evaluated here
     auto stage = [&](int t0, float* buf, int tid, int nthreads) {
         const int ct = min(C, len - t0);
         float* sq = buf;
-        float* sk = sq + C * DK;
-        float* sw = sk + C * DK;
+        float* sk = sq + C * DKP;
+        float* sw = sk + C * DKP;
         float* sv = sw + extra;
         if (MODE == TW_REC_RETENTION) {
             // a rotated pair (i, i + half) at a time: one angle, four loads, four values
@@ -118,30 +129,62 @@ linear_recurrence_kernel(RecArgs a) {
                 const float k1 = tw_to_float(kr[i]), k2 = tw_to_float(kr[i + half]);
                 float sn, cs;
                 sincosf((float)a.positions[row] * a.inv_freq[i], &sn, &cs);
-                sq[t * DK + i] = (q1 * cs - q2 * sn) * a.q_scale;
-                sq[t * DK + i + half] = (q2 * cs + q1 * sn) * a.q_scale;
-                sk[t * DK + i] = (k1 * cs - k2 * sn) * a.k_scale;
-                sk[t * DK + i + half] = (k2 * cs + k1 * sn) * a.k_scale;
+                sq[t * DKP + pad(i)] = (q1 * cs - q2 * sn) * a.q_scale;
+                sq[t * DKP + pad(i + half)] = (q2 * cs + q1 * sn) * a.q_scale;
+                sk[t * DKP + pad(i)] = (k1 * cs - k2 * sn) * a.k_scale;
+                sk[t * DKP + pad(i + half)] = (k2 * cs + k1 * sn) * a.k_scale;
             }
         }
         const int first = MODE == TW_REC_RETENTION ? a.rot_dims : 0;     // channels from here on are not rotated
         const int plain = DK - first;
+        bool staged = false;
+        if constexpr (MODE == TW_REC_DELTA && sizeof(T) == 4 && KS > 1) {
+            if (vec_rows) {
+                // fp32 rows whose heads start on 16-byte boundaries: four channels per load, and all of a thread's
+                // loads of the chunk are under way before the first is used
+                constexpr int V = DK / 4;
+#pragma unroll 2
+                for (int e = tid; e < ct * V; e += nthreads) {
+                    const int t = e / V, i = 4 * (e - t * V);
+                    const size_t row = (size_t)(start + t0 + t);
+                    float4 qq = *reinterpret_cast<const float4*>((const float*)gq + row * a.q_stride + hq * DK + i);
+                    float4 kk = *reinterpret_cast<const float4*>((const float*)gk + row * a.k_stride + hq * DK + i);
+                    qq.x *= a.q_scale; qq.y *= a.q_scale; qq.z *= a.q_scale; qq.w *= a.q_scale;
+                    kk.x *= a.k_scale; kk.y *= a.k_scale; kk.z *= a.k_scale; kk.w *= a.k_scale;
+                    if (a.channel_decay) {
+                        const float4 dd = *reinterpret_cast<const float4*>(a.wpre + row * a.wpre_stride + h * DK + i);
+                        const float4 bb = *reinterpret_cast<const float4*>(a.p1 + h * DK + i);
+                        float4 ww;
+                        ww.x = expf(-rate * tw_softplus(dd.x + bb.x));
+                        ww.y = expf(-rate * tw_softplus(dd.y + bb.y));
+                        ww.z = expf(-rate * tw_softplus(dd.z + bb.z));
+                        ww.w = expf(-rate * tw_softplus(dd.w + bb.w));
+                        *reinterpret_cast<float4*>(sw + t * DKP + pad(i)) = ww;
+                    }
+                    *reinterpret_cast<float4*>(sq + t * DKP + pad(i)) = qq;
+                    *reinterpret_cast<float4*>(sk + t * DKP + pad(i)) = kk;
+                }
+                staged = true;
+            }
+        }
+        if (!staged) {
 #pragma unroll 4
-        for (int e = tid; e < ct * plain; e += nthreads) {
-            const int t = e / plain, i = first + (e - t * plain);
-            const size_t row = (size_t)(start + t0 + t);
-            sq[t * DK + i] = tw_to_float(gq[row * a.q_stride + hq * DK + i]) * a.q_scale;
-            sk[t * DK + i] = tw_to_float(gk[row * a.k_stride + hq * DK + i]) * a.k_scale;
-            if (MODE == TW_REC_WKV)
-                sw[t * DK + i] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
-            if (MODE == TW_REC_DELTA && a.channel_decay)
-                sw[t * DK + i] = expf(-expf(a.p0[h]) * tw_softplus(a.wpre[row * a.wpre_stride + h * DK + i] + a.p1[h * DK + i]));
+            for (int e = tid; e < ct * plain; e += nthreads) {
+                const int t = e / plain, i = first + (e - t * plain);
+                const size_t row = (size_t)(start + t0 + t);
+                sq[t * DKP + pad(i)] = tw_to_float(gq[row * a.q_stride + hq * DK + i]) * a.q_scale;
+                sk[t * DKP + pad(i)] = tw_to_float(gk[row * a.k_stride + hq * DK + i]) * a.k_scale;
+                if (MODE == TW_REC_WKV)
+                    sw[t * DKP + pad(i)] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
+                if (MODE == TW_REC_DELTA && a.channel_decay)
+                    sw[t * DKP + pad(i)] = expf(-rate * tw_softplus(a.wpre[row * a.wpre_stride + h * DK + i] + a.p1[h * DK + i]));
+            }
         }
         if (MODE == TW_REC_DELTA) {
-            float* sg = sw + C * DK;        // [C] the head's decay (where it has one for all channels), [C] the write strength
+            float* sg = sw + C * DKP;       // [C] the head's decay (where it has one for all channels), [C] the write strength
             for (int t = tid; t < ct; t += nthreads) {
                 const size_t row = (size_t)(start + t0 + t);
-                if (!a.channel_decay) sg[t] = expf(-expf(a.p0[h]) * tw_softplus(a.wpre[row * a.wpre_stride + h] + a.p1[h]));
+                if (!a.channel_decay) sg[t] = expf(-rate * tw_softplus(a.wpre[row * a.wpre_stride + h] + a.p1[h]));
                 sg[C + t] = 1.0f / (1.0f + expf(-a.bpre[row * a.bpre_stride + h]));
             }
         }
@@ -167,7 +210,7 @@ linear_recurrence_kernel(RecArgs a) {
     }
     if (MODE == TW_REC_MLSTM) m = slot[(size_t)DK * cols];
     if (MODE == TW_REC_WKV) {
-        for (int i = threadIdx.x; i < DK; i += blockDim.x) su[i] = a.p1[h * DK + i];
+        for (int i = threadIdx.x; i < DK; i += blockDim.x) su[pad(i)] = a.p1[h * DK + i];
     }
     const float decay = MODE == TW_REC_RETENTION ? a.p0[h] : 0.f;
     const int stagers = (int)blockDim.x - per * KS;  // threads that own no column
@@ -182,13 +225,13 @@ linear_recurrence_kernel(RecArgs a) {
         if (!walks && more) stage(t0 + C, next, threadIdx.x - per * KS, stagers);
         if (walks) {                                 // (threads of a live warp whose column lies beyond the last take part in its shuffles)
             const float* sq = buf;
-            const float* sk = sq + C * DK;
-            const float* sw = sk + C * DK;
+            const float* sk = sq + C * DKP;
+            const float* sw = sk + C * DKP;
             const float* sv = sw + extra;
             // ---- the recurrence, token by token
             for (int t = 0; t < ct; ++t) {
-                const float* q = sq + t * DK + ks * SK;
-                const float* k = sk + t * DK + ks * SK;
+                const float* q = sq + t * DKP + ks * SEG;
+                const float* k = sk + t * DKP + ks * SEG;
                 const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : (j < Dv ? sv[t * per + jl] : 0.f);
                 // four partial sums (key channels i mod 4), added at the end: the same order in every step, whatever its size
                 float acc4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -200,21 +243,45 @@ linear_recurrence_kernel(RecArgs a) {
                     fb = expf(li - m_new) * vj;
                     m = m_new;
                 }
-                const float* w = sw + t * DK + ks * SK;
-                const float* u = su + ks * SK;
+                const float* w = sw + t * DKP + ks * SEG;
+                const float* u = su + ks * SEG;
                 if constexpr (MODE == TW_REC_DELTA) {
                     // one pass: decay the column, and form its products with k and with q, and k . q (four partial sums
                     // each over the key channels i mod 4, the same order in every step)
-                    const float gh = a.channel_decay ? 1.f : sw[C * DK + t];
-                    const float beta = sw[C * DK + C + t];
+                    const float gh = a.channel_decay ? 1.f : sw[C * DKP + t];
+                    const float beta = sw[C * DKP + C + t];
                     float r4[4] = {0.f, 0.f, 0.f, 0.f}, d4[4] = {0.f, 0.f, 0.f, 0.f};
+                    if constexpr (SK % 4 == 0) {     // 16-byte reads of the staged rows; the sums are formed as below
+                        const float4* q4 = reinterpret_cast<const float4*>(q);
+                        const float4* k4 = reinterpret_cast<const float4*>(k);
+                        const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll
-                    for (int i = 0; i < SK; ++i) {
-                        const float g = a.channel_decay ? w[i] : gh;
-                        S[i] *= g;
-                        r4[i & 3] += S[i] * k[i];
-                        acc4[i & 3] += S[i] * q[i];
-                        d4[i & 3] += k[i] * q[i];
+                        for (int i4 = 0; i4 < SK / 4; ++i4) {
+                            const float4 qq = q4[i4], kk = k4[i4];
+                            const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
+                            float ga[4] = {gh, gh, gh, gh};
+                            if (a.channel_decay) {
+                                const float4 ww = w4[i4];
+                                ga[0] = ww.x; ga[1] = ww.y; ga[2] = ww.z; ga[3] = ww.w;
+                            }
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int i = 4 * i4 + e;
+                                S[i] *= ga[e];
+                                r4[e] += S[i] * ka[e];
+                                acc4[e] += S[i] * qa[e];
+                                d4[e] += ka[e] * qa[e];
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < SK; ++i) {
+                            const float g = a.channel_decay ? w[i] : gh;
+                            S[i] *= g;
+                            r4[i & 3] += S[i] * k[i];
+                            acc4[i & 3] += S[i] * q[i];
+                            d4[i & 3] += k[i] * q[i];
+                        }
                     }
                     float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
                     float p = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
@@ -228,8 +295,18 @@ linear_recurrence_kernel(RecArgs a) {
                         d += __shfl_xor_sync(0xffffffffu, d, 16);
                     }
                     const float uj = beta * (vj - r);
+                    if constexpr (SK % 4 == 0) {
+                        const float4* k4 = reinterpret_cast<const float4*>(k);
 #pragma unroll
-                    for (int i = 0; i < SK; ++i) S[i] += k[i] * uj;
+                        for (int i4 = 0; i4 < SK / 4; ++i4) {
+                            const float4 kk = k4[i4];
+                            S[4 * i4] += kk.x * uj; S[4 * i4 + 1] += kk.y * uj;
+                            S[4 * i4 + 2] += kk.z * uj; S[4 * i4 + 3] += kk.w * uj;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < SK; ++i) S[i] += k[i] * uj;
+                    }
                     if (live && ks == 0)
                         a.out[(size_t)(start + t0 + t) * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = p + uj * d;
                     continue;
@@ -326,10 +403,10 @@ static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, c
     if (per > ((cols + 31) / 32) * 32) per = ((cols + 31) / 32) * 32;
     RecArgs b = a;
     b.cols_per_block = per;
-    const size_t chunk = 2 * TW_REC_CHUNK * TW_DK + (size_t)TW_REC_CHUNK * per
-                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_DK
-                            : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : (MODE == TW_REC_DELTA ? TW_REC_CHUNK * TW_DK + 2 * TW_REC_CHUNK : 0)));
-    const size_t smem = (2 * chunk + TW_DK) * sizeof(float);
+    const size_t chunk = 2 * TW_REC_CHUNK * TW_REC_DKP + (size_t)TW_REC_CHUNK * per
+                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_REC_DKP
+                            : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : (MODE == TW_REC_DELTA ? TW_REC_CHUNK * TW_REC_DKP + 2 * TW_REC_CHUNK : 0)));
+    const size_t smem = (2 * chunk + TW_REC_DKP) * sizeof(float);
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(linear_recurrence_kernel<T, MODE>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
