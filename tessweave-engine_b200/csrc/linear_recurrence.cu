@@ -18,8 +18,8 @@
 //                      o = (gS)^T q + u (k . q), so one pass over the column gives (gS)^T k, (gS)^T q and k . q.
 //
 // One block per (head, request, slice of the columns of S): a thread owns a column of S in registers (TW_DK
-// values, a compile-time size; where that size is a multiple of 16 four lanes share a column, a quarter of its key
-// channels each) and walks the request's rows of this step in order (the columns of a head are
+// values, a compile-time size; where that size is a multiple of 16 four or eight lanes share a column, a quarter or
+// an eighth of its key channels each) and walks the request's rows of this step in order (the columns of a head are
 // independent of one another, so a head is spread over as many blocks as it takes to fill the GPU; in steps with
 // long portions the block's other warps stage the next 16 tokens meanwhile); the rows of 16 tokens at a time are staged in
 // shared memory as fp32 (rotation, scaling, decays and gates are evaluated there, once per value).  The
@@ -32,11 +32,13 @@
 #define TW_DK 64
 #endif
 #define TW_REC_CHUNK 16
-// Threads that share a column of the state: each owns TW_DK / TW_REC_KSPLIT of its key channels (lanes l, l + 8,
-// l + 16, l + 24 of a warp), and their partial outputs are added by two shuffles.
-#define TW_REC_KSPLIT ((TW_DK % 16 == 0) ? 4 : 1)
-#define TW_REC_SEG (TW_DK / TW_REC_KSPLIT + (TW_REC_KSPLIT > 1 ? 4 : 0))
-#define TW_REC_DKP (TW_REC_SEG * TW_REC_KSPLIT)
+// A column's sums over the key channels are formed in TW_REC_SHARES shares of consecutive channels (four partial sums
+// per share over the channels i mod 4, then the shares pairwise: neighbours, then neighbouring pairs, ...).  KS threads
+// share a column, each with TW_REC_SHARES / KS of the shares (a warp serves 32 / KS columns; lanes l, l + that many, ...
+// share one) and add across threads by shuffles in the same pairing: steps with long portions run KS = 8 where the key
+// size allows (half the chain per token), steps of single tokens KS = 4 (wider reads of the state), and both give the
+// same bits.
+#define TW_REC_SHARES ((TW_DK % 32 == 0) ? 8 : ((TW_DK % 16 == 0) ? 4 : 1))
 
 enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2, TW_REC_DELTA = 3 };
 
@@ -69,14 +71,15 @@ __device__ __forceinline__ float tw_softplus(float x) {
     return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, int KS>
 __global__ void __launch_bounds__(512)
 linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sm[];
-    constexpr int DK = TW_DK, C = TW_REC_CHUNK, KS = TW_REC_KSPLIT, SK = DK / KS;
+    constexpr int DK = TW_DK, C = TW_REC_CHUNK, SK = DK / KS;
+    constexpr int NSH = KS > 1 ? TW_REC_SHARES / KS : 1, SH = SK / NSH;    // shares per thread, channels per share
     // A staged row keeps the KS shares of its key channels four floats apart (SEG = SK + 4), so that the four 16-byte
     // reads a warp issues at once (one per share) fall into different banks; DKP is the padded row.
-    constexpr int SEG = TW_REC_SEG, DKP = TW_REC_DKP;
+    constexpr int SEG = SK + (KS > 1 ? 4 : 0), DKP = SEG * KS;
     auto pad = [](int i) { return KS > 1 ? i + 4 * (i / SK) : i; };
     tw_grid_wait();
     tw_grid_launch_dependents();
@@ -86,10 +89,11 @@ linear_recurrence_kernel(RecArgs a) {
     const int start = a.seq_q_start[s];
     const int Dv = a.Dv, cols = MODE == TW_REC_MLSTM ? Dv + 1 : Dv;
     const int per = a.cols_per_block;
-    // the block's first per * KS threads walk the state: with KS = 4 a warp serves 8 columns (lane & 7) and a lane the
-    // key channels [ks * SK, (ks + 1) * SK) with ks = lane >> 3; with KS = 1 a thread serves a whole column
-    const int jl = KS == 1 ? (int)threadIdx.x : (int)(threadIdx.x >> 5) * 8 + (int)(threadIdx.x & 7);
-    const int ks = KS == 1 ? 0 : (int)(threadIdx.x & 31) >> 3;
+    // the block's first per * KS threads walk the state: with KS > 1 a warp serves CPW = 32 / KS columns (lane % CPW) and
+    // a lane the key channels [ks * SK, (ks + 1) * SK) with ks = lane / CPW; with KS = 1 a thread serves a whole column
+    constexpr int CPW = 32 / KS;
+    const int jl = KS == 1 ? (int)threadIdx.x : (int)(threadIdx.x >> 5) * CPW + (int)(threadIdx.x & (CPW - 1));
+    const int ks = KS == 1 ? 0 : (int)(threadIdx.x & 31) / CPW;
     const int j = blockIdx.z * per + jl;
     const bool walks = (int)threadIdx.x < per * KS;  // the threads that own (a share of) a column; the others only stage rows
     const bool live = walks && j < cols;
@@ -251,27 +255,35 @@ linear_recurrence_kernel(RecArgs a) {
                     const float gh = a.channel_decay ? 1.f : sw[C * DKP + t];
                     const float beta = sw[C * DKP + C + t];
                     float r4[4] = {0.f, 0.f, 0.f, 0.f}, d4[4] = {0.f, 0.f, 0.f, 0.f};
-                    if constexpr (SK % 4 == 0) {     // 16-byte reads of the staged rows; the sums are formed as below
+                    float rs[NSH], ps[NSH], ds[NSH];
+                    if constexpr (SH % 4 == 0) {     // 16-byte reads of the staged rows; share by share
                         const float4* q4 = reinterpret_cast<const float4*>(q);
                         const float4* k4 = reinterpret_cast<const float4*>(k);
                         const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll
-                        for (int i4 = 0; i4 < SK / 4; ++i4) {
-                            const float4 qq = q4[i4], kk = k4[i4];
-                            const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
-                            float ga[4] = {gh, gh, gh, gh};
-                            if (a.channel_decay) {
-                                const float4 ww = w4[i4];
-                                ga[0] = ww.x; ga[1] = ww.y; ga[2] = ww.z; ga[3] = ww.w;
-                            }
+                        for (int sh = 0; sh < NSH; ++sh) {
+                            float rr[4] = {0.f, 0.f, 0.f, 0.f}, pp[4] = {0.f, 0.f, 0.f, 0.f}, dd[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int i = 4 * i4 + e;
-                                S[i] *= ga[e];
-                                r4[e] += S[i] * ka[e];
-                                acc4[e] += S[i] * qa[e];
-                                d4[e] += ka[e] * qa[e];
+                            for (int i4 = sh * (SH / 4); i4 < (sh + 1) * (SH / 4); ++i4) {
+                                const float4 qq = q4[i4], kk = k4[i4];
+                                const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
+                                float ga[4] = {gh, gh, gh, gh};
+                                if (a.channel_decay) {
+                                    const float4 ww = w4[i4];
+                                    ga[0] = ww.x; ga[1] = ww.y; ga[2] = ww.z; ga[3] = ww.w;
+                                }
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int i = 4 * i4 + e;
+                                    S[i] *= ga[e];
+                                    rr[e] += S[i] * ka[e];
+                                    pp[e] += S[i] * qa[e];
+                                    dd[e] += ka[e] * qa[e];
+                                }
                             }
+                            rs[sh] = (rr[0] + rr[1]) + (rr[2] + rr[3]);
+                            ps[sh] = (pp[0] + pp[1]) + (pp[2] + pp[3]);
+                            ds[sh] = (dd[0] + dd[1]) + (dd[2] + dd[3]);
                         }
                     } else {
 #pragma unroll
@@ -286,13 +298,19 @@ linear_recurrence_kernel(RecArgs a) {
                     float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
                     float p = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
                     float d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+                    if constexpr (SH % 4 == 0) {
+                        static_assert(NSH == 1 || NSH == 2, "a thread holds one share or two neighbours");
+                        r = NSH == 2 ? rs[0] + rs[NSH - 1] : rs[0];
+                        p = NSH == 2 ? ps[0] + ps[NSH - 1] : ps[0];
+                        d = NSH == 2 ? ds[0] + ds[NSH - 1] : ds[0];
+                    }
                     if (KS > 1) {
-                        r += __shfl_xor_sync(0xffffffffu, r, 8);
-                        p += __shfl_xor_sync(0xffffffffu, p, 8);
-                        d += __shfl_xor_sync(0xffffffffu, d, 8);
-                        r += __shfl_xor_sync(0xffffffffu, r, 16);
-                        p += __shfl_xor_sync(0xffffffffu, p, 16);
-                        d += __shfl_xor_sync(0xffffffffu, d, 16);
+#pragma unroll
+                        for (int o = CPW; o < 32; o <<= 1) {
+                            r += __shfl_xor_sync(0xffffffffu, r, o);
+                            p += __shfl_xor_sync(0xffffffffu, p, o);
+                            d += __shfl_xor_sync(0xffffffffu, d, o);
+                        }
                     }
                     const float uj = beta * (vj - r);
                     if constexpr (SK % 4 == 0) {
@@ -311,13 +329,17 @@ linear_recurrence_kernel(RecArgs a) {
                         a.out[(size_t)(start + t0 + t) * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = p + uj * d;
                     continue;
                 }
-                if constexpr (SK % 4 == 0) {
+                float share_sum[NSH];
+                if constexpr (SH % 4 == 0) {
                     const float4* q4 = reinterpret_cast<const float4*>(q);
                     const float4* k4 = reinterpret_cast<const float4*>(k);
                     const float4* w4 = reinterpret_cast<const float4*>(w);
                     const float4* u4 = reinterpret_cast<const float4*>(u);
 #pragma unroll
-                    for (int i4 = 0; i4 < SK / 4; ++i4) {
+                    for (int sh = 0; sh < NSH; ++sh) {
+                    acc4[0] = acc4[1] = acc4[2] = acc4[3] = 0.f;
+#pragma unroll
+                    for (int i4 = sh * (SH / 4); i4 < (sh + 1) * (SH / 4); ++i4) {
                         const float4 qq = q4[i4], kk = k4[i4];
                         const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
                         float wa[4] = {0.f, 0.f, 0.f, 0.f}, ua[4] = {0.f, 0.f, 0.f, 0.f};
@@ -342,6 +364,8 @@ linear_recurrence_kernel(RecArgs a) {
                             }
                         }
                     }
+                    share_sum[sh] = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+                    }
                 } else {
 #pragma unroll
                     for (int i = 0; i < SK; ++i) {
@@ -359,9 +383,10 @@ linear_recurrence_kernel(RecArgs a) {
                     }
                 }
                 float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+                if constexpr (SH % 4 == 0) acc = NSH == 2 ? share_sum[0] + share_sum[NSH - 1] : share_sum[0];
                 if (KS > 1) {                        // the shares of a column, always added in this order
-                    acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-                    acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+#pragma unroll
+                    for (int o = CPW; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                 }
                 const size_t row = (size_t)(start + t0 + t);
                 if (live && ks == 0) {
@@ -392,29 +417,38 @@ linear_recurrence_kernel(RecArgs a) {
     }
 }
 
-template <typename T, int MODE>
-static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, cudaStream_t stream) {
+template <typename T, int MODE, int KS>
+static int launch_split(const RecArgs& a, int n_seqs, bool long_portions, cudaStream_t stream) {
     const int cols = MODE == TW_REC_MLSTM ? a.Dv + 1 : a.Dv;
     // columns per block: as many as still give the GPU a block per SM, at least a warp's worth.  A block has four
     // warps at least: all of them stage the rows (loads, rotation, decays), the first `per` threads walk the state
-    constexpr int KS = TW_REC_KSPLIT;
-    int per = KS == 1 ? 128 : 64;
-    while (per > 32 && (long long)a.H * n_seqs * ((cols + per - 1) / per) < 148) per >>= 1;
+    constexpr int SEG = TW_DK / KS + (KS > 1 ? 4 : 0), DKP = SEG * KS;
+    int per = KS == 1 ? 128 : 256 / KS;          // (per * KS walking threads and 256 that stage fit a block of 512)
+    const int least = KS == 8 ? 16 : 32;
+    while (per > least && (long long)a.H * n_seqs * ((cols + per - 1) / per) < 148) per >>= 1;
     if (per > ((cols + 31) / 32) * 32) per = ((cols + 31) / 32) * 32;
     RecArgs b = a;
     b.cols_per_block = per;
-    const size_t chunk = 2 * TW_REC_CHUNK * TW_REC_DKP + (size_t)TW_REC_CHUNK * per
-                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_REC_DKP
-                            : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : (MODE == TW_REC_DELTA ? TW_REC_CHUNK * TW_REC_DKP + 2 * TW_REC_CHUNK : 0)));
-    const size_t smem = (2 * chunk + TW_REC_DKP) * sizeof(float);
+    const size_t chunk = 2 * TW_REC_CHUNK * DKP + (size_t)TW_REC_CHUNK * per
+                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * DKP
+                            : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : (MODE == TW_REC_DELTA ? TW_REC_CHUNK * DKP + 2 * TW_REC_CHUNK : 0)));
+    const size_t smem = (2 * chunk + DKP) * sizeof(float);
     if (smem > 48 * 1024) {
-        const cudaError_t e = cudaFuncSetAttribute(linear_recurrence_kernel<T, MODE>,
+        const cudaError_t e = cudaFuncSetAttribute(linear_recurrence_kernel<T, MODE, KS>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     // steps of single tokens stage one chunk and walk it: a thread per column; longer portions get warps that only stage
     const int threads = long_portions ? per * KS + 256 : per * KS;
-    return tw_launch(linear_recurrence_kernel<T, MODE>, dim3(a.H, n_seqs, (cols + per - 1) / per), dim3(threads), smem, stream, 1, b);
+    return tw_launch(linear_recurrence_kernel<T, MODE, KS>, dim3(a.H, n_seqs, (cols + per - 1) / per), dim3(threads), smem, stream, 1, b);
+}
+
+template <typename T, int MODE>
+static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, cudaStream_t stream) {
+    if constexpr (TW_REC_SHARES == 8) {
+        if (!long_portions) return launch_split<T, MODE, 4>(a, n_seqs, long_portions, stream);
+    }
+    return launch_split<T, MODE, TW_REC_SHARES>(a, n_seqs, long_portions, stream);
 }
 
 TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void* q, int q_stride, const void* k, int k_stride,
