@@ -387,6 +387,90 @@ short_conv_kernel(float* __restrict__ out, const T* __restrict__ x, int x_stride
     for (int c = max(c0, unit_end) + threadIdx.x; c < c1; c += blockDim.x) orow[c] = sy[c - c0];
 }
 
+// The same for steps with many rows and at most TW_CONV_FAST_TAPS taps: a block serves `rows_per_block` consecutive rows
+// of the step, a thread keeps the last inputs of its channel in registers while it walks down the rows (an input is
+// loaded once, not once per tap; the taps' weights once per block), and one barrier serves all the rows.  The taps
+// are added in the same order as above, so both kernels give the same bits.
+#define TW_CONV_FAST_TAPS 4
+#define TW_CONV_ROWS 8
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(256)
+short_conv_rows_kernel(float* __restrict__ out, const T* __restrict__ x, int x_stride, const float* __restrict__ w,
+                       float* __restrict__ state, long long state_stride, long long state_offset,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
+                       const int* __restrict__ seq_q_len, int move_single, int n_rows, int channels, int chunk, int unit_heads,
+                       int unit_dim, int scaled_heads, float head_scale, float unit_eps) {
+    extern __shared__ float sy[];        // [TW_CONV_ROWS][chunk]
+    constexpr int R = TW_CONV_ROWS;
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int row0 = blockIdx.x * R;
+    const int nr = min(R, n_rows - row0);
+    const int c0 = blockIdx.y * chunk, c1 = min(channels, c0 + chunk);
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+        float wt[TAPS], xw[TAPS];
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wt[j] = w[(size_t)c * TAPS + j];
+        // xw[j] is the input TAPS - 1 - j rows before the current one (whichever request that row belongs to)
+#pragma unroll
+        for (int j = 0; j + 1 < TAPS; ++j) {
+            const int rr = row0 - (TAPS - 1) + j;
+            xw[j] = rr >= 0 ? tw_to_float(x[(size_t)rr * x_stride + c]) : 0.f;
+        }
+        float xr[R];                     // the block's rows of this channel, all asked for before the first is used
+#pragma unroll
+        for (int i = 0; i < R; ++i) xr[i] = i < nr ? tw_to_float(x[(size_t)(row0 + i) * x_stride + c]) : 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            if (i >= nr) break;
+            const int row = row0 + i;
+            xw[TAPS - 1] = xr[i];
+            const int s = seq_of_token[row];
+            if (s >= 0) {
+                const int r = row - seq_q_start[s];          // rows of this request before this one in the step
+                float* tc = state + (size_t)seq_slot[s] * state_stride + state_offset + (size_t)c * (TAPS - 1);
+                const bool move = move_single && TAPS > 1 && seq_q_len[s] == 1;
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < TAPS; ++j) {
+                    const int back = TAPS - 1 - j;
+                    const float xv = back <= r ? xw[j] : tc[TAPS - 1 + r - back];
+                    acc += wt[j] * xv;
+                    if (move && j > 0) tc[j - 1] = xv;
+                }
+                sy[i * chunk + (c - c0)] = acc / (1.0f + expf(-acc));
+            }
+#pragma unroll
+            for (int j = 0; j + 1 < TAPS; ++j) xw[j] = xw[j + 1];
+        }
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int unit_end = unit_heads * unit_dim;
+    const int h0 = unit_dim > 0 ? c0 / unit_dim : 0;
+    const int h1 = c0 < unit_end ? min(unit_heads, (c1 + unit_dim - 1) / unit_dim) : h0;
+    const int nh = h1 - h0;
+    for (int pair = warp; pair < nr * nh; pair += nwarps) {
+        const int i = pair / nh, head = h0 + (pair - i * nh);
+        if (seq_of_token[row0 + i] < 0) continue;
+        const float* y = sy + i * chunk + (head * unit_dim - c0);
+        float ss = 0.f;
+        for (int d = lane; d < unit_dim; d += 32) ss += y[d] * y[d];
+        ss = tw_warp_sum(ss);
+        const float f = (head < scaled_heads ? head_scale : 1.0f) / sqrtf(ss + unit_eps);
+        float* orow = out + (size_t)(row0 + i) * channels;
+        for (int d = lane; d < unit_dim; d += 32) orow[head * unit_dim + d] = y[d] * f;
+    }
+    const int p0 = max(c0, unit_end);
+    if (p0 < c1) {
+        const int span = c1 - p0;
+        for (int e = threadIdx.x; e < nr * span; e += blockDim.x) {
+            const int i = e / span, c = p0 + (e - i * span);
+            if (seq_of_token[row0 + i] >= 0) out[(size_t)(row0 + i) * channels + c] = sy[i * chunk + (c - c0)];
+        }
+    }
+}
+
 // The convolution's state after the step: the last taps - 1 inputs of every request, older ones kept where the
 // step brought fewer rows than that.  One thread per (request, channel) reads its old values before it writes.
 template <typename T>
@@ -422,6 +506,28 @@ static int launch_short_conv(float* out, const T* x, int x_stride, const float* 
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(short_conv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+    }
+    if (n_rows >= 8 * TW_CONV_ROWS && taps <= TW_CONV_FAST_TAPS && smem * TW_CONV_ROWS <= 96 * 1024) {
+        const size_t rsmem = smem * TW_CONV_ROWS;
+        const dim3 rgrid((n_rows + TW_CONV_ROWS - 1) / TW_CONV_ROWS, (channels + chunk - 1) / chunk);
+#define TW_CONV_ROWS_LAUNCH(TAPS)                                                                                                \
+        {                                                                                                                        \
+            if (rsmem > 48 * 1024) {                                                                                             \
+                const cudaError_t e = cudaFuncSetAttribute(short_conv_rows_kernel<T, TAPS>,                                      \
+                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rsmem);             \
+                if (e != cudaSuccess) return (int)e;                                                                             \
+            }                                                                                                                    \
+            return tw_launch(short_conv_rows_kernel<T, TAPS>, rgrid, dim3(256), rsmem, stream, 1, out, x, x_stride, w, state,    \
+                             state_stride, state_offset, seq_of_token, seq_slot, seq_q_start, seq_q_len, move_single, n_rows,   \
+                             channels, chunk, unit_heads, unit_dim, scaled_heads, head_scale, unit_eps);                         \
+        }
+        switch (taps) {
+        case 1: TW_CONV_ROWS_LAUNCH(1)
+        case 2: TW_CONV_ROWS_LAUNCH(2)
+        case 3: TW_CONV_ROWS_LAUNCH(3)
+        default: TW_CONV_ROWS_LAUNCH(4)
+        }
+#undef TW_CONV_ROWS_LAUNCH
     }
     const dim3 grid(n_rows, (channels + chunk - 1) / chunk);
     return tw_launch(short_conv_kernel<T>, grid, dim3(256), smem, stream, 1, out, x, x_stride, w, taps, state, state_stride,

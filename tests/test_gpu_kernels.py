@@ -958,3 +958,56 @@ def test_decode_attention_tma_refuses_and_reports():
     o.attention_decode_tma(out, q, None, None, None, False, args[0], args[1], args[2], args[3], table, *args[5:], 2, scratch,
                            counters, st)
     assert int(st) == 2
+
+
+# ---------------------------------------------------------------------------
+# short causal convolution with silu and unit heads, over mixed batches, against plain torch
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 6])
+@pytest.mark.parametrize("lengths", [[1, 70, 3, 1, 40], [5, 1, 2], [200], [1] * 66])
+def test_short_convolution_over_a_mixed_batch(dtype, taps, lengths):
+    """Requests of one row (whose state the kernel moves on itself), of fewer rows than taps, and of many rows, in
+    one step, each on a state that earlier steps left; steps with few rows and with many (a block per row, or a block
+    per eight rows with the last inputs in registers).  Padding rows (request -1) are left alone."""
+    from tessweave_engine_b200.csrc import ops
+    dev, dt = torch.device("cuda"), DTYPES[dtype]
+    g = torch.Generator().manual_seed(taps * 100 + len(lengths))
+    channels, unit_heads, unit_dim, scaled = 104, 3, 16, 1
+    keep, offset, n_seqs = taps - 1, 5, len(lengths)
+    n = sum(lengths)
+    pad = 3
+    x = (torch.randn(n + pad, channels + 2, generator=g) * 0.8).to(dt)
+    w = torch.randn(channels, taps, generator=g) * 0.5
+    slots = torch.randperm(n_seqs + 2, generator=g)[:n_seqs].to(torch.int32)
+    state = torch.randn(n_seqs + 2, offset + channels * keep + 1, generator=g)
+    starts = torch.tensor([sum(lengths[:i]) for i in range(n_seqs)], dtype=torch.int32)
+    lens = torch.tensor(lengths, dtype=torch.int32)
+    seq_of = torch.cat([torch.full((L,), i, dtype=torch.int32) for i, L in enumerate(lengths)] + [torch.full((pad,), -1, dtype=torch.int32)])
+    # plain: the request's old inputs, then its rows
+    want = torch.zeros(n, channels, dtype=torch.float64)
+    want_state = state.clone().double()
+    xd = x.double()[:, :channels]
+    for i, L in enumerate(lengths):
+        old = state[slots[i], offset:offset + channels * keep].double().view(channels, keep).t()      # [keep, channels], oldest first
+        rows = torch.cat([old, xd[starts[i]:starts[i] + L]])
+        for t in range(L):
+            acc = (rows[t:t + taps] * w.double().t()).sum(0)
+            want[starts[i] + t] = acc * torch.sigmoid(acc)
+        if keep:
+            want_state[slots[i], offset:offset + channels * keep] = rows[L:L + keep].t().reshape(-1)
+    heads = want[:, :unit_heads * unit_dim].view(n, unit_heads, unit_dim)
+    heads = heads / torch.sqrt((heads ** 2).sum(-1, keepdim=True) + 1e-6)
+    heads[:, :scaled] *= 0.25
+    want[:, :unit_heads * unit_dim] = heads.reshape(n, -1)
+    out = torch.full((n + pad, channels), 7.0, device=dev)
+    st = state.to(dev)
+    args = [t.to(dev) for t in (seq_of, slots, starts)]
+    ops.short_conv(out, x.to(dev), w.to(dev), st, offset, *args, n + pad, unit_heads=unit_heads, unit_dim=unit_dim,
+                   scaled_heads=scaled, head_scale=0.25, unit_eps=1e-6, move_single=lens.to(dev))
+    if keep:
+        ops.short_conv_state(x.to(dev), taps, channels, st, offset, slots.to(dev), starts.to(dev), lens.to(dev), n_seqs, skip_single=True)
+    torch.cuda.synchronize()
+    assert float((out[:n].cpu().double() - want).abs().max()) <= 2e-5
+    assert bool((out[n:] == 7.0).all()), "padding rows were written"
+    assert float((st.cpu().double() - want_state).abs().max()) <= 1e-6, "the convolutions' last inputs"
