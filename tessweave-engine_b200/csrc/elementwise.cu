@@ -1002,6 +1002,68 @@ TW_EXPORT int tw_scaled_accumulate(float* acc, void* out, const void* x, float s
 }
 
 // ---------------------------------------------------------------------------
+// out[n] = sum_m scale_m * x_m[n] (weights null), or sum_m scale_m * x_m[n] / sqrt(mean(x_m[n]^2) + eps) * weight_m, for up
+// to TW_SUM_MEMBERS members whose rows lie in buffers of their own: one pass, statistics and sum in fp32 (the members
+// are added in their order), one rounding.  A row is read twice, the second time from cache.
+// ---------------------------------------------------------------------------
+#define TW_SUM_MEMBERS 4
+struct SumMembers {
+    const void* x[TW_SUM_MEMBERS];
+    float scale[TW_SUM_MEMBERS];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(TW_NORM_THREADS)
+weighted_sum_rows_kernel(T* __restrict__ out, const SumMembers in, const float* __restrict__ weights, float eps, int members,
+                         int width) {
+    __shared__ float scratch[33];
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const size_t base = (size_t)blockIdx.x * width;
+    float f[TW_SUM_MEMBERS];
+#pragma unroll
+    for (int m = 0; m < TW_SUM_MEMBERS; ++m) {
+        f[m] = in.scale[m];
+        if (m < members && weights) {        // (the same for every thread of the block)
+            const T* x = (const T*)in.x[m] + base;
+            float ss = 0.f;
+            for (int c = threadIdx.x; c < width; c += blockDim.x) {
+                const float v = tw_to_float(x[c]);
+                ss += v * v;
+            }
+            ss = tw_block_sum(ss, scratch);
+            f[m] = in.scale[m] / sqrtf(ss / (float)width + eps);
+        }
+    }
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll
+        for (int m = 0; m < TW_SUM_MEMBERS; ++m) {
+            if (m < members) {
+                const float v = tw_to_float(((const T*)in.x[m])[base + c]);
+                acc += weights ? v * f[m] * weights[(size_t)m * width + c] : f[m] * v;
+            }
+        }
+        out[base + c] = tw_from_float<T>(acc);
+    }
+}
+
+TW_EXPORT int tw_weighted_sum_rows(void* out, const void* x0, const void* x1, const void* x2, const void* x3, float s0, float s1,
+                                   float s2, float s3, const float* weights, float eps, int members, int n_rows, int width,
+                                   int dtype, cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    if (members < 1 || members > TW_SUM_MEMBERS) return (int)cudaErrorInvalidValue;
+    SumMembers in;
+    in.x[0] = x0; in.x[1] = x1; in.x[2] = x2; in.x[3] = x3;
+    in.scale[0] = s0; in.scale[1] = s1; in.scale[2] = s2; in.scale[3] = s3;
+    if (dtype == TW_F32)
+        return tw_launch(weighted_sum_rows_kernel<float>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, (float*)out, in,
+                         weights, eps, members, width);
+    return tw_launch(weighted_sum_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1,
+                     (__nv_bfloat16*)out, in, weights, eps, members, width);
+}
+
+// ---------------------------------------------------------------------------
 // resid[n, :] += vec for the first n_rows rows: a learned vector added to every row of the fp32 residual stream.
 // ---------------------------------------------------------------------------
 __global__ void add_row_vector_kernel(float* __restrict__ resid, const float* __restrict__ vec, int width, size_t count) {

@@ -1544,6 +1544,30 @@ def normed_accumulate(acc: torch.Tensor, out: torch.Tensor | None, x: torch.Tens
     _check(code, "normed_accumulate")
 
 
+WEIGHTED_SUM_MAX_MEMBERS = 4
+
+
+def weighted_sum_rows(out: torch.Tensor, members: list[torch.Tensor], scales: list[float], weights: torch.Tensor | None,
+                      eps: float, n_rows: int) -> None:
+    """out[r] = sum_m scales[m] * members[m][r], or with ``weights`` ([members, width] fp32) the same over rows that are
+    first divided by their root mean square (``eps`` inside the root) and multiplied by ``weights[m]``; fp32 statistics
+    and sum, members added in their order, one rounding.  The members lie in buffers of their own."""
+    _cuda(out, weights, *members)
+    k, width = len(members), out.shape[1]
+    _need(1 <= k <= WEIGHTED_SUM_MAX_MEMBERS and len(scales) == k, f"weighted_sum_rows: 1 to {WEIGHTED_SUM_MAX_MEMBERS} members, a scale each")
+    _need(out.is_contiguous() and out.shape[0] >= n_rows
+          and all(x.dtype == out.dtype and x.is_contiguous() and x.shape[1] == width and x.shape[0] >= n_rows
+                  and x.data_ptr() != out.data_ptr() for x in members),
+          "weighted_sum_rows: rows of one type and width, contiguous, none of them the result")
+    _need(weights is None or (weights.dtype == torch.float32 and weights.is_contiguous() and tuple(weights.shape) == (k, width)),
+          "weighted_sum_rows: the weights must be fp32 [members, width]")
+    xs = [_ptr(x) for x in members] + [_ptr(None)] * (WEIGHTED_SUM_MAX_MEMBERS - k)
+    sc = [c_float(float(v)) for v in scales] + [c_float(0.0)] * (WEIGHTED_SUM_MAX_MEMBERS - k)
+    code = _fn("elementwise", "tw_weighted_sum_rows")(_ptr(out), *xs, *sc, _ptr(weights), c_float(float(eps or 0.0)), c_int(k),
+                                                      c_int(n_rows), c_int(width), c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "weighted_sum_rows")
+
+
 SHORT_CONV_MAX_TAPS = 17
 
 

@@ -479,14 +479,13 @@ def nufatar_kernel_table(config: dict, batch: int, context: int, prefill_tokens:
             m * H * Dv * 8, 0.0, reps=8)
         del sets
         # ---- the normalised sum of the two sides
-        sets = [(torch.empty(m, W, device=dev), torch.empty(m, W, device=dev, dtype=bf), torch.randn(m, W, device=dev, dtype=bf),
-                 torch.randn(m, W, device=dev, dtype=bf)) for _ in range(_copies(m * W * 14))]
-        nw = torch.ones(W, device=dev)
+        sets = [(torch.empty(m, W, device=dev, dtype=bf), torch.randn(m, W, device=dev, dtype=bf),
+                 torch.randn(m, W, device=dev, dtype=bf)) for _ in range(_copies(m * W * 6))]
+        nw = torch.ones(2, W, device=dev)
 
-        def both(acc, out, x, y):
-            ops.normed_accumulate(acc, None, x, nw, 1e-6, 0.5, first=True, n_rows=m)
-            ops.normed_accumulate(acc, out, y, nw, 1e-6, 0.5, first=False, n_rows=m)
-        add(f"{phase}: RMSNorm of each side + half their sum", m, [(lambda s=s: both(*s)) for s in sets], m * W * (2 + 4 + 2 + 4 + 4 + 2), 0.0, reps=8)
+        def both(out, x, y):
+            ops.weighted_sum_rows(out, [x, y], [0.5, 0.5], nw, 1e-6, m)
+        add(f"{phase}: RMSNorm of each side + half their sum", m, [(lambda s=s: both(*s)) for s in sets], m * W * (2 + 2 + 2), 0.0, reps=8)
         del sets
         torch.cuda.empty_cache()
     if int(status) != 0:

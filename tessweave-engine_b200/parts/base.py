@@ -146,6 +146,7 @@ class Workspace:
         self.device = device
         self._buffers: dict[str, torch.Tensor] = {}
         self.frozen = False
+        self.prefix = ""        # put before every name: a part that runs several parts side by side gives each buffers of its own
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """The buffer ``name`` with at least ``shape`` elements.  ``zero`` fills it with zeros when it
@@ -153,6 +154,7 @@ class Workspace:
         numel = 1
         for s in shape:
             numel *= int(s)
+        name = self.prefix + name
         buf = self._buffers.get(name)
         if buf is None or buf.dtype != dtype or buf.numel() < numel:
             if self.frozen:

@@ -58,9 +58,21 @@ class WeightedSumMixer(Mixer):
     def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
         if not isinstance(cache, SeveralViews) or len(cache.views) != len(self.members):
             raise TypeError("weighted_sum needs one cache view per member")
-        n, dt = ctx.n_tokens, self.runtime.dtype
-        acc = ctx.workspace.get("weighted_sum.acc", (n, self.hidden), torch.float32)
-        out = ctx.workspace.get("weighted_sum.delta", (n, self.hidden), dt)
+        n, dt, ws = ctx.n_tokens, self.runtime.dtype, ctx.workspace
+        out = ws.get("weighted_sum.delta", (n, self.hidden), dt)
+        if len(self.members) <= ops.WEIGHTED_SUM_MAX_MEMBERS:
+            # every member works in workspace buffers of its own, so that all results exist side by side; one kernel
+            # normalises (where asked), scales and adds them
+            deltas, outer = [], ws.prefix
+            for i, (member, view) in enumerate(zip(self.members, cache.views)):
+                ws.prefix = f"{outer}member{i}."
+                try:
+                    deltas.append(dense_delta(ctx, member.forward(ctx, h, view, write_cache), dt)[:n])
+                finally:
+                    ws.prefix = outer
+            ops.weighted_sum_rows(out, deltas, self.scales, self.norm_weights, self.norm_eps, n)
+            return out
+        acc = ws.get("weighted_sum.acc", (n, self.hidden), torch.float32)
         last = len(self.members) - 1
         for i, (member, scale, view) in enumerate(zip(self.members, self.scales, cache.views)):
             delta = dense_delta(ctx, member.forward(ctx, h, view, write_cache), dt)[:n]
