@@ -63,7 +63,7 @@ TW_EXPORT int tw_embed(void* resid, const void* table, const int* ids, const int
 
 // ---------------------------------------------------------------------------
 // Residual add + RMSNorm.
-//   v = resid[src] + delta[src]            (delta may be null)
+//   v = resid[src] + delta_scale * delta[src]     (delta may be null; the product and the sum are fp32)
 //   resid[src] = v                         (only when rows == null)
 //   out[r] = T( (v * (1 / sqrt(mean(v^2) + eps))) * weight )
 // rows != null selects source rows (the final norm runs on the wanted rows
@@ -82,7 +82,7 @@ template <typename T, bool ONE_PASS>
 __global__ void __launch_bounds__(TW_NORM_THREADS)
 add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
                    const float* __restrict__ partial, int nsplit, size_t split_stride,
-                   const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
+                   const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows, float dscale) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     TW_TIMELINE_SCOPE(TW_K_NORM);
@@ -95,7 +95,7 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __re
     const float* ps = partial ? partial + (size_t)src * hidden : nullptr;
     const bool has_delta = d || ps;
     auto delta_at = [&](int i) -> float {
-        if (d) return tw_to_float(d[i]);
+        if (d) return tw_to_float(d[i]) * dscale;
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;      // fixed order: ((s0 + s1) + (s2 + s3)) over interleaved slices
         int k = 0;
         for (; k + 4 <= nsplit; k += 4) {
@@ -105,7 +105,7 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __re
             s3 += ps[(size_t)(k + 3) * split_stride + i];
         }
         for (; k < nsplit; ++k) s0 += ps[(size_t)k * split_stride + i];
-        return (s0 + s1) + (s2 + s3);
+        return ((s0 + s1) + (s2 + s3)) * dscale;
     };
     T* o = out + (size_t)r * hidden;
     if (ONE_PASS) {
@@ -159,7 +159,7 @@ template <typename T>
 __global__ void __launch_bounds__(TW_NORM_CTHREADS)
 add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
                            const float* __restrict__ partial, int nsplit, size_t split_stride,
-                           const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
+                           const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows, float dscale) {
     __shared__ float scratch[33];
     __shared__ float all_ss[TW_NORM_CLUSTER];      // every block's sum of squares, written here by the blocks themselves
     TW_TIMELINE_SCOPE(TW_K_NORM_CLUSTER);
@@ -222,7 +222,7 @@ add_rmsnorm_cluster_kernel(T* __restrict__ out, float* __restrict__ resid, const
                 for (k = max(k, full); k < nsplit; ++k) sum[0] += ps[(size_t)k * split_stride + i];
                 dv = (sum[0] + sum[1]) + (sum[2] + sum[3]);
             }
-            v[j] = x[i] + dv;
+            v[j] = x[i] + dv * dscale;
             if (!rows && has_delta) x[i] = v[j];
             ss += v[j] * v[j];
         }
@@ -266,7 +266,7 @@ __device__ __forceinline__ void tw_store4(__nv_bfloat16* p, float4 v) {
 template <typename T, int V4>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T* __restrict__ delta,
-                        const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows) {
+                        const float* __restrict__ weight, float eps, int hidden, const int* __restrict__ rows, float dscale) {
     __shared__ float scratch[33];
     TW_TIMELINE_SCOPE(TW_K_NORM);
     tw_grid_wait();
@@ -286,7 +286,7 @@ add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T*
             v[j] = x4[i];
             if (delta) {
                 const float4 d = tw_load4(delta + (size_t)src * hidden + 4 * i);
-                v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+                v[j].x += d.x * dscale; v[j].y += d.y * dscale; v[j].z += d.z * dscale; v[j].w += d.w * dscale;
                 if (!rows) x4[i] = v[j];
             }
             ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
@@ -309,39 +309,39 @@ add_rmsnorm_vec4_kernel(T* __restrict__ out, float* __restrict__ resid, const T*
 template <typename T>
 static int launch_add_rmsnorm(T* out, float* resid, const T* delta, const float* partial, int nsplit,
                               size_t split_stride, const float* weight, float eps, int n_rows, int hidden,
-                              const int* rows, cudaStream_t stream) {
+                              const int* rows, float dscale, cudaStream_t stream) {
     if (n_rows <= 64 && hidden >= 1024 && hidden <= TW_NORM_CLUSTER * TW_NORM_CTHREADS * TW_NORM_CMAXV) {
         return tw_launch(add_rmsnorm_cluster_kernel<T>, dim3(n_rows * TW_NORM_CLUSTER), dim3(TW_NORM_CTHREADS), 0, stream,
-                         TW_NORM_CLUSTER, out, resid, delta, partial, nsplit, split_stride, weight, eps, hidden, rows);
+                         TW_NORM_CLUSTER, out, resid, delta, partial, nsplit, split_stride, weight, eps, hidden, rows, dscale);
     }
     if (!partial && (hidden & 3) == 0 && hidden <= 4 * 256 * TW_NORM_V4) {
         if (hidden <= 4 * 256 * 4)
             tw_launch(add_rmsnorm_vec4_kernel<T, 4>, dim3(n_rows), dim3(256), 0, stream, 1, out, resid, delta, weight, eps,
-                      hidden, rows);
+                      hidden, rows, dscale);
         else
             tw_launch(add_rmsnorm_vec4_kernel<T, TW_NORM_V4>, dim3(n_rows), dim3(256), 0, stream, 1, out, resid, delta, weight,
-                      eps, hidden, rows);
+                      eps, hidden, rows, dscale);
         return TW_LAUNCH_CHECK();
     }
     if (hidden <= TW_NORM_THREADS * TW_NORM_MAXV)
         tw_launch(add_rmsnorm_kernel<T, true>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, out, resid, delta, partial, nsplit,
-                                                                            split_stride, weight, eps, hidden, rows);
+                                                                            split_stride, weight, eps, hidden, rows, dscale);
     else
         tw_launch(add_rmsnorm_kernel<T, false>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, out, resid, delta, partial, nsplit,
-                                                                             split_stride, weight, eps, hidden, rows);
+                                                                             split_stride, weight, eps, hidden, rows, dscale);
     return TW_LAUNCH_CHECK();
 }
 
 TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const float* partial, int nsplit,
                              long split_stride, const float* weight, float eps, int n_rows, int hidden,
-                             const int* rows, int dtype, cudaStream_t stream) {
+                             const int* rows, float delta_scale, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (delta && partial) return (int)cudaErrorInvalidValue;
     if (dtype == TW_F32)
         return launch_add_rmsnorm<float>((float*)out, resid, (const float*)delta, partial, nsplit, (size_t)split_stride,
-                                         weight, eps, n_rows, hidden, rows, stream);
+                                         weight, eps, n_rows, hidden, rows, delta_scale, stream);
     return launch_add_rmsnorm<__nv_bfloat16>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, partial, nsplit,
-                                             (size_t)split_stride, weight, eps, n_rows, hidden, rows, stream);
+                                             (size_t)split_stride, weight, eps, n_rows, hidden, rows, delta_scale, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -718,15 +718,15 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
 }
 
 // ---------------------------------------------------------------------------
-// Rotation of pairs in place, on the first `n_heads` heads of each packed row and the first `rot_dims`
-// values of a head: angle = float(position) * inv_freq[i]; pair i is (2i, 2i+1) when `interleaved`, else
-// (i, i + rot_dims / 2); cos and sin are both multiplied by `magnitude`.  The general form of the rotation above, for
+// Rotation of pairs in place, on the first `n_heads` heads of each packed row and `rot_dims` values of a head
+// from value `first` on: angle = float(position) * inv_freq[i]; pair i is (first + 2i, first + 2i+1) when
+// `interleaved`, else (first + i, first + i + rot_dims / 2); cos and sin are both multiplied by `magnitude`.  The general form of the rotation above, for
 // encodings no fused kernel takes.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void rotate_pairs_kernel(T* __restrict__ rows, int row_stride, const int* __restrict__ positions,
                                     const int* __restrict__ seq_of_token, const float* __restrict__ inv_freq, int n_heads,
-                                    int D, int rot_dims, int interleaved, float magnitude) {
+                                    int D, int first, int rot_dims, int interleaved, float magnitude) {
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int n = blockIdx.x;
@@ -736,7 +736,7 @@ __global__ void rotate_pairs_kernel(T* __restrict__ rows, int row_stride, const 
     T* row = rows + (size_t)n * row_stride;
     for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < n_heads * half; idx += gridDim.y * blockDim.x) {
         const int head = idx / half, i = idx - head * half;
-        const int a = head * D + (interleaved ? 2 * i : i), b = head * D + (interleaved ? 2 * i + 1 : i + half);
+        const int a = head * D + first + (interleaved ? 2 * i : i), b = head * D + first + (interleaved ? 2 * i + 1 : i + half);
         float sn, cs;
         sincosf((float)pos * inv_freq[i], &sn, &cs);
         sn *= magnitude;
@@ -748,17 +748,123 @@ __global__ void rotate_pairs_kernel(T* __restrict__ rows, int row_stride, const 
 }
 
 TW_EXPORT int tw_rotate_pairs(void* rows, int row_stride, const int* positions, const int* seq_of_token,
-                              const float* inv_freq, int n_tokens, int n_heads, int D, int rot_dims, int interleaved,
-                              float magnitude, int dtype, cudaStream_t stream) {
+                              const float* inv_freq, int n_tokens, int n_heads, int D, int first, int rot_dims,
+                              int interleaved, float magnitude, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || rot_dims < 2) return 0;
-    if (rot_dims > D || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
+    if (first < 0 || first + rot_dims > D || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
     const int work = n_heads * (rot_dims / 2);
     const dim3 grid(n_tokens, (work + 127) / 128 < 8 ? (work + 127) / 128 : 8);
     if (dtype == TW_F32)
         return tw_launch(rotate_pairs_kernel<float>, grid, dim3(128), 0, stream, 1, (float*)rows, row_stride, positions,
-                         seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved, magnitude);
+                         seq_of_token, inv_freq, n_heads, D, first, rot_dims, interleaved, magnitude);
     return tw_launch(rotate_pairs_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, (__nv_bfloat16*)rows, row_stride,
-                     positions, seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved, magnitude);
+                     positions, seq_of_token, inv_freq, n_heads, D, first, rot_dims, interleaved, magnitude);
+}
+
+// ---------------------------------------------------------------------------
+// RMS norm of spans of columns, in place: span s is `heads[s]` heads of `dim[s]` values from column `col[s]` on, and
+// every head is normalised on its own, x <- x / sqrt(mean(x^2) + eps) * weight[s][i], with one weight [dim] for all
+// heads of a span.  Statistics, quotient and product are fp32; one rounding to the rows' type.  Serves the
+// per-head norms of queries and keys (two spans: the query heads, the key heads) and the norms of low-rank
+// latents (a span of one head).  A warp per head.
+// ---------------------------------------------------------------------------
+struct NormSpans {
+    int count;
+    int col[2], heads[2], dim[2];
+    const float* weight[2];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+span_rmsnorm_kernel(T* __restrict__ rows, int row_stride, NormSpans sp, float eps, int n_rows, int heads_total) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= (long)n_rows * heads_total) return;
+    const int row = (int)(item / heads_total);
+    int head = (int)(item - (long)row * heads_total), s = 0;
+    if (head >= sp.heads[0]) { head -= sp.heads[0]; s = 1; }
+    const int D = sp.dim[s];
+    T* x = rows + (size_t)row * row_stride + sp.col[s] + (size_t)head * D;
+    const float* w = sp.weight[s];
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+        const float v = tw_to_float(x[i]);
+        ss += v * v;
+    }
+    ss = tw_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int i = lane; i < D; i += 32) x[i] = tw_from_float<T>((tw_to_float(x[i]) * inv) * w[i]);
+}
+
+TW_EXPORT int tw_span_rmsnorm(void* rows, int row_stride, int n_rows, int spans, int col0, int heads0, int dim0,
+                              const float* weight0, int col1, int heads1, int dim1, const float* weight1, float eps,
+                              int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (spans < 1 || spans > 2 || heads0 <= 0 || dim0 <= 0 || !weight0 || (spans == 2 && (heads1 <= 0 || dim1 <= 0 || !weight1)))
+        return (int)cudaErrorInvalidValue;
+    NormSpans sp;
+    sp.count = spans;
+    sp.col[0] = col0; sp.heads[0] = heads0; sp.dim[0] = dim0; sp.weight[0] = weight0;
+    sp.col[1] = col1; sp.heads[1] = spans == 2 ? heads1 : 0; sp.dim[1] = dim1; sp.weight[1] = weight1;
+    const int total = sp.heads[0] + sp.heads[1];
+    const dim3 grid((unsigned)(((size_t)n_rows * total + 3) / 4));
+    if (dtype == TW_F32)
+        return tw_launch(span_rmsnorm_kernel<float>, grid, dim3(128), 0, stream, 1, (float*)rows, row_stride, sp, eps, n_rows, total);
+    return tw_launch(span_rmsnorm_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, (__nv_bfloat16*)rows, row_stride, sp, eps,
+                     n_rows, total);
+}
+
+// ---------------------------------------------------------------------------
+// out[r, c] = x[r, c] * act(gate[r, c]) with act = sigmoid (1) or silu (2): an output gate on a mixer's heads.
+// fp32 arithmetic, one rounding.  x, gate and out may be column slices of wider rows (strides in elements).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_mul_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ x, int x_stride,
+                                const T* __restrict__ gate, int gate_stride, int cols, long total, int act) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long step = (long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += step) {
+        const long r = idx / cols;
+        const int c = (int)(idx - r * cols);
+        const float g = tw_to_float(gate[r * gate_stride + c]);
+        const float sg = 1.0f / (1.0f + expf(-g));
+        out[r * out_stride + c] = tw_from_float<T>(tw_to_float(x[r * x_stride + c]) * (act == 2 ? g * sg : sg));
+    }
+}
+
+TW_EXPORT int tw_gate_mul(void* out, int out_stride, const void* x, int x_stride, const void* gate, int gate_stride, int n_rows,
+                          int cols, int act, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0 || cols <= 0) return 0;
+    if (act != 1 && act != 2) return (int)cudaErrorInvalidValue;
+    const long total = (long)n_rows * cols;
+    const int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+    if (dtype == TW_F32)
+        return tw_launch(gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (float*)out, out_stride, (const float*)x,
+                         x_stride, (const float*)gate, gate_stride, cols, total, act);
+    return tw_launch(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, out_stride,
+                     (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate, gate_stride, cols, total, act);
+}
+
+// ---------------------------------------------------------------------------
+// Soft cap of fp32 logits in place: x <- cap * tanh(x / cap).
+// ---------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ x, long total, float cap) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long step = (long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += step) x[idx] = cap * tanhf(x[idx] / cap);
+}
+
+TW_EXPORT int tw_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    const int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+    return tw_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, 1, x, (long)total, cap);
 }
 
 // ---------------------------------------------------------------------------

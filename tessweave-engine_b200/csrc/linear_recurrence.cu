@@ -1,6 +1,6 @@
 // Linear attention as a recurrence over a matrix state of fixed size per request and head.
 //
-// A head keeps S [Dk, Dv] in fp32.  Three update rules share one kernel (rows q/r, k [Dk], v [Dv] per token):
+// A head keeps S [Dk, Dv] in fp32.  Several update rules share one kernel (rows q/r, k [Dk], v [Dv] per token):
 //
 //   TW_REC_RETENTION   S <- g S + k v^T                     o = S^T q          g a constant per head
 //                      q and k are rotated by position on the way in, k is scaled after the rotation
@@ -16,6 +16,9 @@
 //                      prepared (here: convolved, activated, scaled to unit length); heads of v may share a head of q
 //                      and k (qk_group value heads per q/k head).  The read-out sees the token's own write:
 //                      o = (gS)^T q + u (k . q), so one pass over the column gives (gS)^T k, (gS)^T q and k . q.
+//   TW_REC_GLA         S <- diag(a) S + k v^T                o = S^T q          (gated linear attention)
+//                      a = sigmoid(z + b)^(1 / tau) per key channel from the projected z, evaluated as
+//                      exp(logsigmoid(z + b) / tau); 1 / tau arrives in `cap`, b in p0
 //
 // One block per (head, request, slice of the columns of S): a thread owns a column of S in registers (TW_DK
 // values, a compile-time size; where that size is a multiple of 16 four or eight lanes share a column, a quarter or
@@ -40,7 +43,7 @@
 // same bits.
 #define TW_REC_SHARES ((TW_DK % 32 == 0) ? 8 : ((TW_DK % 16 == 0) ? 4 : 1))
 
-enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2, TW_REC_DELTA = 3 };
+enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2, TW_REC_DELTA = 3, TW_REC_GLA = 4 };
 
 struct RecArgs {
     float* out;                 // [rows, H * Dv] fp32
@@ -48,8 +51,8 @@ struct RecArgs {
     const void* q; int q_stride;        // rows of q (r), k, v: element type T, column h * D + i inside each
     const void* k; int k_stride;
     const void* v; int v_stride;
-    const float* wpre; int wpre_stride; // wkv: d [rows, H * Dk] fp32;  mlstm: [rows, 2 H] fp32 (pi | pf);  delta: d [rows, H * Dk] or [rows, H]
-    const float* p0;            // wkv: w0 [H * Dk];  retention: decay [H];  mlstm: bias [2 H];  delta: A [H] (log of the rate)
+    const float* wpre; int wpre_stride; // wkv, gla: d [rows, H * Dk] fp32;  mlstm: [rows, 2 H] fp32 (pi | pf);  delta: d [rows, H * Dk] or [rows, H]
+    const float* p0;            // wkv: w0 [H * Dk];  gla: b [H * Dk];  retention: decay [H];  mlstm: bias [2 H];  delta: A [H] (log of the rate)
     const float* p1;            // wkv: u [H * Dk];  delta: b [H * Dk] or [H]
     const float* bpre; int bpre_stride; // delta: the write strength's pre-activation [rows, H] fp32
     int channel_decay;          // delta: a decay per key channel (else one per head)
@@ -99,7 +102,7 @@ linear_recurrence_kernel(RecArgs a) {
     const bool live = walks && j < cols;
     // a staged chunk: q [C][DK], k [C][DK], w [C][DK] (wkv) or gates [C][2] (mlstm), v [C][per]; two of them, so that
     // the rows of the next 16 tokens are staged while the state walks through these
-    const int extra = MODE == TW_REC_WKV ? C * DKP : (MODE == TW_REC_MLSTM ? 2 * C : (MODE == TW_REC_DELTA ? C * DKP + 2 * C : 0));
+    const int extra = (MODE == TW_REC_WKV || MODE == TW_REC_GLA) ? C * DKP : (MODE == TW_REC_MLSTM ? 2 * C : (MODE == TW_REC_DELTA ? C * DKP + 2 * C : 0));
     const int chunk_floats = 2 * C * DKP + extra + C * per;
     float* su = sm + 2 * chunk_floats;      // [DKP] bonus (wkv)
     const long long head_state = (long long)DK * cols + (MODE == TW_REC_MLSTM ? 1 : 0);
@@ -180,6 +183,8 @@ linear_recurrence_kernel(RecArgs a) {
                 sk[t * DKP + pad(i)] = tw_to_float(gk[row * a.k_stride + hq * DK + i]) * a.k_scale;
                 if (MODE == TW_REC_WKV)
                     sw[t * DKP + pad(i)] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
+                if (MODE == TW_REC_GLA)
+                    sw[t * DKP + pad(i)] = expf(tw_logsigmoid(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]) * a.cap);
                 if (MODE == TW_REC_DELTA && a.channel_decay)
                     sw[t * DKP + pad(i)] = expf(-rate * tw_softplus(a.wpre[row * a.wpre_stride + h * DK + i] + a.p1[h * DK + i]));
             }
@@ -348,6 +353,10 @@ linear_recurrence_kernel(RecArgs a) {
                             wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w;
                             ua[0] = uu.x; ua[1] = uu.y; ua[2] = uu.z; ua[3] = uu.w;
                         }
+                        if (MODE == TW_REC_GLA) {
+                            const float4 ww = w4[i4];
+                            wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w;
+                        }
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int i = 4 * i4 + e;
@@ -358,6 +367,9 @@ linear_recurrence_kernel(RecArgs a) {
                                 const float kv = ka[e] * vj;
                                 acc4[e] += qa[e] * (S[i] + ua[e] * kv);
                                 S[i] = wa[e] * S[i] + kv;
+                            } else if (MODE == TW_REC_GLA) {
+                                S[i] = wa[e] * S[i] + ka[e] * vj;
+                                acc4[e] += qa[e] * S[i];
                             } else {
                                 S[i] = fa * S[i] + fb * ka[e];
                                 acc4[e] += qa[e] * S[i];
@@ -376,6 +388,9 @@ linear_recurrence_kernel(RecArgs a) {
                             const float kv = k[i] * vj;
                             acc4[i & 3] += q[i] * (S[i] + u[i] * kv);
                             S[i] = w[i] * S[i] + kv;
+                        } else if (MODE == TW_REC_GLA) {
+                            S[i] = w[i] * S[i] + k[i] * vj;
+                            acc4[i & 3] += q[i] * S[i];
                         } else {
                             S[i] = fa * S[i] + fb * k[i];
                             acc4[i & 3] += q[i] * S[i];
@@ -430,7 +445,7 @@ static int launch_split(const RecArgs& a, int n_seqs, bool long_portions, cudaSt
     RecArgs b = a;
     b.cols_per_block = per;
     const size_t chunk = 2 * TW_REC_CHUNK * DKP + (size_t)TW_REC_CHUNK * per
-                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * DKP
+                         + ((MODE == TW_REC_WKV || MODE == TW_REC_GLA) ? TW_REC_CHUNK * DKP
                             : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : (MODE == TW_REC_DELTA ? TW_REC_CHUNK * DKP + 2 * TW_REC_CHUNK : 0)));
     const size_t smem = (2 * chunk + DKP) * sizeof(float);
     if (smem > 48 * 1024) {
@@ -483,6 +498,10 @@ TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void*
     case TW_REC_MLSTM:
         return f32 ? launch_recurrence<float, TW_REC_MLSTM>(a, n_seqs, lp, stream)
                    : launch_recurrence<__nv_bfloat16, TW_REC_MLSTM>(a, n_seqs, lp, stream);
+    case TW_REC_GLA:
+        if (!wpre || !p0) return (int)cudaErrorInvalidValue;
+        return f32 ? launch_recurrence<float, TW_REC_GLA>(a, n_seqs, lp, stream)
+                   : launch_recurrence<__nv_bfloat16, TW_REC_GLA>(a, n_seqs, lp, stream);
     case TW_REC_DELTA:
         if (!f32 || !bpre || !wpre || !p0 || !p1) return (int)cudaErrorInvalidValue;     // its rows are prepared in fp32 in every run type
         return launch_recurrence<float, TW_REC_DELTA>(a, n_seqs, lp, stream);

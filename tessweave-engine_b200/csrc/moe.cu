@@ -4,9 +4,15 @@
 //
 //   tw_moe_route     z = Wr h + br (fp32); the `top` largest z (lowest index first at a tie); their weights are the
 //                    softmax over those alone; optionally one more dot product per token, sigmoid(ws . h), the
-//                    gate of an expert that every token uses
+//                    gate of an expert that every token uses.  With `scoring` 1: s = softmax(z) over every router
+//                    output, the `top` largest s + correction are chosen, and their weights are s * weight_scale
+//                    (not renormalised)
 //   tw_moe_gate_up   act[token, j] = silu(Wg_e h) * (Wu_e h)          e = the j-th expert of the token
+//                    with `act` 1: g = min(Wg_e h, limit), u = clamp(Wu_e h, -limit, limit), g sigmoid(alpha g) (u + 1)
 //   tw_moe_down      out[token] = sum_j weight_j Wd_e act[token, j]  (+ gate * shared[token])
+//
+// The router may have more outputs than there are experts with matrices: outputs E .. E + identity - 1 are identity
+// experts, whose output is the token's row itself (times the weight); they read no matrix.
 //
 // Expert matrices are stacked: gate/up [E, 2, F, width] (a gate matrix followed by its up matrix), down
 // [E, width, F].  Dot products accumulate in fp32; the weighted sum over experts is fp32.
@@ -96,7 +102,8 @@ template <typename T>
 __global__ void __launch_bounds__(512)
 moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, float* __restrict__ shared_gate,
                  const T* __restrict__ h, int h_stride, const T* __restrict__ wr, const float* __restrict__ br,
-                 const T* __restrict__ ws, int width, int E, int top) {
+                 const T* __restrict__ ws, int width, int E, int top, int scoring, const float* __restrict__ correction,
+                 float weight_scale) {
     extern __shared__ float sm[];           // [width] the row, [E + 1] logits, [E] marks
     tw_grid_wait();
     tw_grid_launch_dependents();
@@ -116,6 +123,26 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, float* __
     // selection: `top` times the largest logit that is left; a row of NaN still names `top` different experts
     float* taken = z + E + 1;
     for (int e = 0; e < E; ++e) taken[e] = 0.f;
+    if (scoring == 1) {
+        // scores over every output; the choice looks at score + correction, the weight is the plain score
+        float top_z = -INFINITY, den = 0.f;
+        for (int e = 0; e < E; ++e) top_z = fmaxf(top_z, z[e]);
+        for (int e = 0; e < E; ++e) { z[e] = expf(z[e] - top_z); den += z[e]; }
+        for (int e = 0; e < E; ++e) z[e] /= den;
+        for (int j = 0; j < top; ++j) {
+            int arg = -1;
+            float best = -INFINITY;
+            for (int e = 0; e < E; ++e) {
+                if (taken[e] != 0.f) continue;
+                const float c = z[e] + (correction ? correction[e] : 0.f);
+                if (arg < 0 || c > best) { arg = e; best = c; }
+            }
+            taken[arg] = 1.f;
+            chosen[(size_t)row * top + j] = arg;
+            weight[(size_t)row * top + j] = z[arg] * weight_scale;
+        }
+        return;
+    }
     float best0 = 0.f, sum = 0.f;
     for (int j = 0; j < top; ++j) {
         int arg = -1;
@@ -135,26 +162,40 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, float* __
 }
 
 TW_EXPORT int tw_moe_route(int* chosen, float* weight, float* shared_gate, const void* h, int h_stride, const void* wr,
-                           const float* br, const void* ws, int rows, int width, int E, int top, int dtype,
-                           cudaStream_t stream) {
+                           const float* br, const void* ws, int rows, int width, int E, int top, int scoring,
+                           const float* correction, float weight_scale, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E) return (int)cudaErrorInvalidValue;
+    if (E <= 0 || top <= 0 || top > E || scoring < 0 || scoring > 1) return (int)cudaErrorInvalidValue;
     const size_t smem = ((size_t)width + 2 * E + 1) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     const int threads = 32 * min(16, max(4, E + 1));        // a warp per expert (and one for the shared gate), up to 16
     if (dtype == TW_F32)
         return tw_launch(moe_route_kernel<float>, dim3(rows), dim3(threads), smem, stream, 1, chosen, weight, shared_gate,
-                         (const float*)h, h_stride, (const float*)wr, br, (const float*)ws, width, E, top);
+                         (const float*)h, h_stride, (const float*)wr, br, (const float*)ws, width, E, top, scoring, correction,
+                         weight_scale);
     return tw_launch(moe_route_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, stream, 1, chosen, weight, shared_gate,
-                     (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)wr, br, (const __nv_bfloat16*)ws, width, E, top);
+                     (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)wr, br, (const __nv_bfloat16*)ws, width, E, top,
+                     scoring, correction, weight_scale);
 }
 
 #define TW_MOE_WARPS 8
 
+// what an expert makes of its gate and up products: 0 silu(g) u;  1 with g = min(g, limit), u = clamp(u, -limit, limit):
+// g sigmoid(alpha g) (u + 1)
+__device__ __forceinline__ float tw_glu(float g, float u, int act, float limit, float alpha) {
+    if (act == 1) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(32 * TW_MOE_WARPS)
 moe_gate_up_kernel(T* __restrict__ act, const T* __restrict__ h, int h_stride, const T* __restrict__ wgu,
-                   const int* __restrict__ chosen, int width, int F, int E, int top, int rows_per_block) {
+                   const int* __restrict__ chosen, int width, int F, int E, int top, int rows_per_block, int glu, float limit,
+                   float alpha) {
     extern __shared__ float sm[];           // [width]
     tw_grid_wait();
     tw_grid_launch_dependents();
@@ -171,12 +212,12 @@ moe_gate_up_kernel(T* __restrict__ act, const T* __restrict__ h, int h_stride, c
     for (int f = f0 + warp; f < f1; f += TW_MOE_WARPS) {
         float g, u;
         tw_dot2<T>(wg + (size_t)f * width, wu + (size_t)f * width, sm, sm, width, lane, vec, g, u);
-        if (lane == 0) act[(size_t)pair * F + f] = tw_from_float<T>(g / (1.0f + expf(-g)) * u);
+        if (lane == 0) act[(size_t)pair * F + f] = tw_from_float<T>(tw_glu(g, u, glu, limit, alpha));
     }
 }
 
 TW_EXPORT int tw_moe_gate_up(void* act, const void* h, int h_stride, const void* wgu, const int* chosen, int rows, int width,
-                             int F, int E, int top, int dtype, cudaStream_t stream) {
+                             int F, int E, int top, int glu, float limit, float alpha, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
@@ -187,16 +228,16 @@ TW_EXPORT int tw_moe_gate_up(void* act, const void* h, int h_stride, const void*
     const dim3 grid(rows * top, (F + per - 1) / per);
     if (dtype == TW_F32)
         return tw_launch(moe_gate_up_kernel<float>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (float*)act, (const float*)h,
-                         h_stride, (const float*)wgu, chosen, width, F, E, top, per);
+                         h_stride, (const float*)wgu, chosen, width, F, E, top, per, glu, limit, alpha);
     return tw_launch(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (__nv_bfloat16*)act,
-                     (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)wgu, chosen, width, F, E, top, per);
+                     (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)wgu, chosen, width, F, E, top, per, glu, limit, alpha);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(32 * TW_MOE_WARPS)
 moe_down_kernel(T* __restrict__ out, const T* __restrict__ act, const T* __restrict__ wd, const int* __restrict__ chosen,
                 const float* __restrict__ weight, const T* __restrict__ shared, const float* __restrict__ shared_gate,
-                int width, int F, int E, int top, int cols_per_block) {
+                int width, int F, int E, int top, int cols_per_block, const T* __restrict__ h, int h_stride, int identity) {
     extern __shared__ float sm[];           // [top][F] the activations of the token's experts
     tw_grid_wait();
     tw_grid_launch_dependents();
@@ -212,7 +253,18 @@ moe_down_kernel(T* __restrict__ out, const T* __restrict__ act, const T* __restr
         int j = 0;
         for (; j + 1 < top; j += 2) {            // two experts' rows side by side; always added in the order of the experts
             const int e0 = chosen[(size_t)row * top + j], e1 = chosen[(size_t)row * top + j + 1];
-            if (e0 < 0 || e0 >= E || e1 < 0 || e1 >= E) continue;
+            if (e0 < 0 || e0 >= E || e1 < 0 || e1 >= E) {
+                if (identity > 0) {          // one of the two has no matrices: each on its own
+                    for (int jj = j; jj < j + 2; ++jj) {
+                        const int e = chosen[(size_t)row * top + jj];
+                        if (e >= E && e < E + identity)
+                            acc += weight[(size_t)row * top + jj] * tw_to_float(h[(size_t)row * h_stride + c]);
+                        else if (e >= 0 && e < E)
+                            acc += weight[(size_t)row * top + jj] * tw_dot<T>(wd + ((size_t)e * width + c) * F, sm + (size_t)jj * F, F, lane, vec);
+                    }
+                }
+                continue;
+            }
             float d0, d1;
             tw_dot2<T>(wd + ((size_t)e0 * width + c) * F, wd + ((size_t)e1 * width + c) * F, sm + (size_t)j * F, sm + (size_t)(j + 1) * F,
                        F, lane, vec, d0, d1);
@@ -221,6 +273,7 @@ moe_down_kernel(T* __restrict__ out, const T* __restrict__ act, const T* __restr
         }
         for (; j < top; ++j) {
             const int e = chosen[(size_t)row * top + j];
+            if (e >= E && e < E + identity) acc += weight[(size_t)row * top + j] * tw_to_float(h[(size_t)row * h_stride + c]);
             if (e < 0 || e >= E) continue;
             acc += weight[(size_t)row * top + j] * tw_dot<T>(wd + ((size_t)e * width + c) * F, sm + (size_t)j * F, F, lane, vec);
         }
@@ -232,9 +285,10 @@ moe_down_kernel(T* __restrict__ out, const T* __restrict__ act, const T* __restr
 }
 
 TW_EXPORT int tw_moe_down(void* out, const void* act, const void* wd, const int* chosen, const float* weight,
-                          const void* shared, const float* shared_gate, int rows, int width, int F, int E, int top, int dtype,
-                          cudaStream_t stream) {
+                          const void* shared, const float* shared_gate, int rows, int width, int F, int E, int top,
+                          const void* h, int h_stride, int identity, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (identity < 0 || (identity > 0 && !h)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)top * F * sizeof(float);
     if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
     int per = width;
@@ -244,23 +298,26 @@ TW_EXPORT int tw_moe_down(void* out, const void* act, const void* wd, const int*
     if (dtype == TW_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return tw_launch(moe_down_kernel<float>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (float*)out, (const float*)act,
-                         (const float*)wd, chosen, weight, (const float*)shared, shared_gate, width, F, E, top, per);
+                         (const float*)wd, chosen, weight, (const float*)shared, shared_gate, width, F, E, top, per,
+                         (const float*)h, h_stride, identity);
     }
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(moe_down_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return tw_launch(moe_down_kernel<__nv_bfloat16>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (__nv_bfloat16*)out,
                      (const __nv_bfloat16*)act, (const __nv_bfloat16*)wd, chosen, weight, (const __nv_bfloat16*)shared,
-                     shared_gate, width, F, E, top, per);
+                     shared_gate, width, F, E, top, per, (const __nv_bfloat16*)h, h_stride, identity);
 }
 
 // ---------------------------------------------------------------------------
 // Steps with many rows: the (token, expert) pairs are sorted by expert, so that each expert's rows stand together
 // and its matrices meet them in one product with many rows.
 //
-//   tw_moe_sort      order[i] = the pair (token * top + j) at sorted place i; place[pair] = its place;
+//   tw_moe_sort      order[i] = the pair (token * top + j) at sorted place i (-1 behind the last group); place[pair] = its place;
 //                    ends[e] = one past the last place of expert e (the prefix sum of the experts' counts)
 //   tw_moe_gather    xs[i] = h[order[i] / top]
-//   tw_moe_combine   out[token] = sum_j weight[token, j] * ys[place[token * top + j]]  (+ gate * shared[token])
+//   tw_moe_combine   out[token] = sum_j weight[token, j] * ys[place[token * top + j]]  (+ gate * shared[token]);
+//                    a pair whose expert is an identity expert has no place and adds weight * h[token]
+//   tw_glu_rows      act = what an expert makes of its gate and up products, over rows [gates | ups]
 //
 // The order of the pairs inside an expert's group is whatever the atomics give; no result depends on it.
 // ---------------------------------------------------------------------------
@@ -287,6 +344,8 @@ moe_sort_kernel(int* __restrict__ order, int* __restrict__ place, int* __restric
         }
     }
     __syncthreads();
+    // places behind the last group (pairs whose expert has no matrices) name no pair
+    for (int p = ends[E - 1] + threadIdx.x; p < pairs; p += blockDim.x) order[p] = -1;
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = chosen[p];
         if (e >= 0 && e < E) {
@@ -312,6 +371,10 @@ __global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ h, i
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int i = blockIdx.x;
+    if (order[i] < 0) {         // a place no pair was sorted into: a row of zeros, which no group's product reads
+        for (int c = threadIdx.x; c < width; c += blockDim.x) xs[(size_t)i * width + c] = tw_from_float<T>(0.f);
+        return;
+    }
     const T* src = h + (size_t)(order[i] / top) * h_stride;
     for (int c = threadIdx.x; c < width; c += blockDim.x) xs[(size_t)i * width + c] = src[c];
 }
@@ -329,7 +392,8 @@ TW_EXPORT int tw_moe_gather(void* xs, const void* h, int h_stride, const int* or
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ys, const int* __restrict__ place,
                                    const float* __restrict__ weight, const T* __restrict__ shared,
-                                   const float* __restrict__ shared_gate, int top, int width) {
+                                   const float* __restrict__ shared_gate, int top, int width, const int* __restrict__ chosen,
+                                   const T* __restrict__ h, int h_stride, int E, int identity) {
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int row = blockIdx.x;
@@ -339,6 +403,10 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ys
         for (int j = 0; j < top; ++j) {
             const int at = place[(size_t)row * top + j];
             if (at >= 0) acc += weight[(size_t)row * top + j] * tw_to_float(ys[(size_t)at * width + c]);
+            else if (identity > 0) {
+                const int e = chosen[(size_t)row * top + j];
+                if (e >= E && e < E + identity) acc += weight[(size_t)row * top + j] * tw_to_float(h[(size_t)row * h_stride + c]);
+            }
         }
         if (shared) acc += sg * tw_to_float(shared[(size_t)row * width + c]);
         out[(size_t)row * width + c] = tw_from_float<T>(acc);
@@ -346,11 +414,41 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ys
 }
 
 TW_EXPORT int tw_moe_combine(void* out, const void* ys, const int* place, const float* weight, const void* shared,
-                             const float* shared_gate, int rows, int top, int width, int dtype, cudaStream_t stream) {
+                             const float* shared_gate, int rows, int top, int width, const int* chosen, const void* h,
+                             int h_stride, int E, int identity, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (identity < 0 || (identity > 0 && (!h || !chosen))) return (int)cudaErrorInvalidValue;
     if (dtype == TW_F32)
         return tw_launch(moe_combine_kernel<float>, dim3(rows), dim3(256), 0, stream, 1, (float*)out, (const float*)ys, place,
-                         weight, (const float*)shared, shared_gate, top, width);
+                         weight, (const float*)shared, shared_gate, top, width, chosen, (const float*)h, h_stride, E, identity);
     return tw_launch(moe_combine_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
-                     (const __nv_bfloat16*)ys, place, weight, (const __nv_bfloat16*)shared, shared_gate, top, width);
+                     (const __nv_bfloat16*)ys, place, weight, (const __nv_bfloat16*)shared, shared_gate, top, width, chosen,
+                     (const __nv_bfloat16*)h, h_stride, E, identity);
+}
+
+template <typename T>
+__global__ void glu_rows_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, long total, int glu, float limit,
+                                float alpha) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long step = (long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += step) {
+        const long n = idx / inter;
+        const int i = (int)(idx - n * inter);
+        out[idx] = tw_from_float<T>(tw_glu(tw_to_float(gate_up[n * 2 * inter + i]), tw_to_float(gate_up[n * 2 * inter + inter + i]),
+                                           glu, limit, alpha));
+    }
+}
+
+TW_EXPORT int tw_glu_rows(void* out, const void* gate_up, int rows, int inter, int glu, float limit, float alpha, int dtype,
+                          cudaStream_t stream) {
+    if (rows <= 0 || inter <= 0) return 0;
+    const long total = (long)rows * inter;
+    const int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+    if (dtype == TW_F32)
+        return tw_launch(glu_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (float*)out, (const float*)gate_up, inter,
+                         total, glu, limit, alpha);
+    return tw_launch(glu_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)gate_up, inter, total, glu, limit, alpha);
 }

@@ -373,8 +373,8 @@ def mingru_scan(out: torch.Tensor, proj: torch.Tensor, bias_z: torch.Tensor | No
 
 
 def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor,
-                eps: float, n_rows: int, rows: torch.Tensor | None = None) -> None:
-    """resid += delta (in place, fp32) and out = rmsnorm(resid) * weight.
+                eps: float, n_rows: int, rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> None:
+    """resid += delta_scale * delta (in place, fp32) and out = rmsnorm(resid) * weight.
 
     ``delta`` is None, a tensor of the output's type, or a ``SplitSum`` (fp32 slices of a
     matrix product split over k, added here in slice order).  With ``rows`` (int32 indices)
@@ -401,7 +401,7 @@ def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Ten
         _need(resid.shape[0] >= n_rows, "rmsnorm: fewer residual rows than asked")
     code = _fn("elementwise", "tw_add_rmsnorm")(_ptr(out), _ptr(resid), _ptr(delta), _ptr(partial), c_int(nsplit),
                                                 c_long(split_stride), _ptr(weight), c_float(eps),
-                                                c_int(n_rows), c_int(hidden), _ptr(rows),
+                                                c_int(n_rows), c_int(hidden), _ptr(rows), c_float(delta_scale),
                                                 c_int(dtype_code(out.dtype)), _stream())
     _check(code, "add_rmsnorm")
 
@@ -463,19 +463,60 @@ def rotate_heads(rows: torch.Tensor, bias: torch.Tensor | None, positions: torch
 
 
 def rotate_pairs(rows: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, inv_freq: torch.Tensor,
-                 n_tokens: int, n_heads: int, head_dim: int, rot_dims: int, interleaved: bool, magnitude: float = 1.0) -> None:
-    """In place on the first ``n_heads`` heads of each packed row: rotate ``rot_dims / 2`` pairs at the start of
-    every head by ``position * inv_freq[i]``; pair i is (2i, 2i+1) when ``interleaved``, else (i, i + rot_dims / 2).
-    cos and sin are both multiplied by ``magnitude``."""
+                 n_tokens: int, n_heads: int, head_dim: int, rot_dims: int, interleaved: bool, magnitude: float = 1.0,
+                 first: int = 0) -> None:
+    """In place on the first ``n_heads`` heads of each packed row: rotate ``rot_dims / 2`` pairs of every head, from
+    the head's value ``first`` on, by ``position * inv_freq[i]``; pair i is (2i, 2i+1) when ``interleaved``, else
+    (i, i + rot_dims / 2), counted from ``first``.  cos and sin are both multiplied by ``magnitude``."""
     _cuda(rows, positions, seq_of_token, inv_freq)
     _need(rows.stride(1) == 1 and rows.shape[1] >= n_heads * head_dim, "rotate_pairs: bad rows")
-    _need(rot_dims % 2 == 0 and 0 <= rot_dims <= head_dim and inv_freq.dtype == torch.float32
-          and inv_freq.numel() == rot_dims // 2, "rotate_pairs: inv_freq must be fp32 [rot_dims / 2], rot_dims even and <= D")
+    _need(rot_dims % 2 == 0 and first >= 0 and 0 <= rot_dims <= head_dim - first and inv_freq.dtype == torch.float32
+          and inv_freq.numel() == rot_dims // 2, "rotate_pairs: inv_freq must be fp32 [rot_dims / 2], rot_dims even and inside the head")
     code = _fn("elementwise", "tw_rotate_pairs")(_ptr(rows), c_int(rows.stride(0)), _ptr(positions), _ptr(seq_of_token),
-                                                 _ptr(inv_freq), c_int(n_tokens), c_int(n_heads), c_int(head_dim),
+                                                 _ptr(inv_freq), c_int(n_tokens), c_int(n_heads), c_int(head_dim), c_int(first),
                                                  c_int(rot_dims), c_int(1 if interleaved else 0), c_float(magnitude),
                                                  c_int(dtype_code(rows.dtype)), _stream())
     _check(code, "rotate_pairs")
+
+
+def span_rmsnorm(rows: torch.Tensor, n_rows: int, spans: list[tuple[int, int, int, torch.Tensor]], eps: float) -> None:
+    """In place: every span ``(first column, heads, head size, weight fp32 [head size])`` of the rows is that many
+    heads side by side, each divided by its own root mean square (eps inside the root) and multiplied by the span's
+    weight, in fp32.  One or two spans per call."""
+    _need(1 <= len(spans) <= 2, "span_rmsnorm: one or two spans")
+    _cuda(rows, *(w for _, _, _, w in spans))
+    _need(rows.dim() == 2 and rows.stride(1) == 1 and rows.shape[0] >= n_rows, "span_rmsnorm: bad rows")
+    for col, heads, dim, w in spans:
+        _need(col >= 0 and heads > 0 and dim > 0 and col + heads * dim <= rows.shape[1] and w.dtype == torch.float32
+              and w.numel() == dim and w.is_contiguous(), "span_rmsnorm: a span must lie inside the rows, with an fp32 weight per value of a head")
+    (c0, h0, d0, w0), (c1, h1, d1, w1) = spans[0], (spans[1] if len(spans) == 2 else (0, 0, 0, None))
+    code = _fn("elementwise", "tw_span_rmsnorm")(_ptr(rows), c_int(rows.stride(0)), c_int(n_rows), c_int(len(spans)), c_int(c0),
+                                                 c_int(h0), c_int(d0), _ptr(w0), c_int(c1), c_int(h1), c_int(d1), _ptr(w1),
+                                                 c_float(eps), c_int(dtype_code(rows.dtype)), _stream())
+    _check(code, "span_rmsnorm")
+
+
+def gate_mul(out: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, act: int, n_rows: int) -> None:
+    """out = x * act(gate) element by element (``GATE_SIGMOID`` or ``GATE_SILU``), fp32 arithmetic; the three may be
+    column slices of wider rows and ``out`` may be ``x``."""
+    _cuda(out, x, gate)
+    cols = out.shape[1]
+    _need(x.shape[1] == cols and gate.shape[1] == cols and out.dtype == x.dtype == gate.dtype
+          and out.stride(1) == x.stride(1) == gate.stride(1) == 1 and min(out.shape[0], x.shape[0], gate.shape[0]) >= n_rows,
+          "gate_mul: three operands of one type and width")
+    _need(act in (GATE_SILU, GATE_SIGMOID), "gate_mul: the activation is silu or sigmoid")
+    code = _fn("elementwise", "tw_gate_mul")(_ptr(out), c_int(out.stride(0)), _ptr(x), c_int(x.stride(0)), _ptr(gate),
+                                             c_int(gate.stride(0)), c_int(n_rows), c_int(cols), c_int(2 if act == GATE_SILU else 1),
+                                             c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "gate_mul")
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place on contiguous fp32 rows."""
+    _cuda(logits)
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and cap > 0, "softcap: contiguous fp32 logits and a positive cap")
+    code = _fn("elementwise", "tw_softcap")(_ptr(logits), ctypes.c_longlong(logits.numel()), c_float(cap), _stream())
+    _check(code, "softcap")
 
 
 def silu_mul(out: torch.Tensor, gate_up, n_rows: int, interleaved: bool = False) -> None:
@@ -1231,7 +1272,7 @@ def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: 
 # ---------------------------------------------------------------------------
 # pieces of mixers that are not attention over a cache: recurrences with a matrix state, token shift
 # ---------------------------------------------------------------------------
-RECURRENCE_RETENTION, RECURRENCE_WKV, RECURRENCE_MLSTM, RECURRENCE_DELTA = 0, 1, 2, 3
+RECURRENCE_RETENTION, RECURRENCE_WKV, RECURRENCE_MLSTM, RECURRENCE_DELTA, RECURRENCE_GLA = 0, 1, 2, 3, 4
 RECURRENCE_MAX_KEY_DIM = 256      # a thread keeps a column of the state in registers (beyond 128 it spills)
 
 
@@ -1260,7 +1301,8 @@ def linear_recurrence(mode: int, out: torch.Tensor, den: torch.Tensor | None, q:
     The delta rule takes fp32 q, k, v that are ready to use, ``pre`` the projected decay ([rows, heads * key_dim] with
     ``channel_decay``, else [rows, heads]), ``p0`` the log of each head's rate [heads], ``p1`` the decay's bias (of
     ``pre``'s width), ``write_pre`` the write strength before its sigmoid, fp32 [rows, heads]; ``qk_group`` value heads
-    share a head of q and k."""
+    share a head of q and k.  Gated linear attention takes ``pre`` the projected decay [rows, heads * key_dim], ``p0`` its
+    bias and ``cap`` the exponent 1 / tau of the sigmoid."""
     _cuda(out, den, q, k, v, state, positions, seq_slot, seq_q_start, seq_q_len, pre, p0, p1, inv_freq, tail, write_pre)
     if mode == RECURRENCE_DELTA:
         width = heads * key_dim if channel_decay else heads
@@ -1278,6 +1320,9 @@ def linear_recurrence(mode: int, out: torch.Tensor, den: torch.Tensor | None, q:
     _need(mode != RECURRENCE_MLSTM or (den is not None and pre is not None and p0 is not None), "recurrence: mlstm needs gates and a denominator buffer")
     _need(mode != RECURRENCE_WKV or (pre is not None and p0 is not None and p1 is not None and key_dim == value_dim), "recurrence: wkv needs decay rows, offset and bonus")
     _need(mode != RECURRENCE_RETENTION or p0 is not None, "recurrence: retention needs a decay per head")
+    _need(mode != RECURRENCE_GLA or (pre is not None and p0 is not None and pre.stride(1) == 1 and pre.shape[1] >= heads * key_dim
+                                     and p0.numel() == heads * key_dim and cap > 0),
+          "recurrence: gated linear attention needs the projected decay rows, their bias and a positive exponent")
     code = _fn("linear_recurrence", "tw_linear_recurrence", {"TW_DK": key_dim})(
         c_int(mode), _ptr(out), _ptr(den), _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), _ptr(v), c_int(v.stride(0)),
         _ptr(pre), c_int(0 if pre is None else pre.stride(0)), _ptr(p0), _ptr(p1), _ptr(write_pre),
@@ -1407,11 +1452,16 @@ def kv_store(rows: torch.Tensor, k_col: int, v_col: int, positions: torch.Tensor
 # routed feed-forward
 # ---------------------------------------------------------------------------
 def moe_route(chosen: torch.Tensor, weight: torch.Tensor, shared_gate: torch.Tensor | None, h: torch.Tensor, w_router: torch.Tensor,
-              b_router: torch.Tensor | None, w_shared_gate: torch.Tensor | None, n_rows: int, top: int) -> None:
+              b_router: torch.Tensor | None, w_shared_gate: torch.Tensor | None, n_rows: int, top: int,
+              score_all: bool = False, correction: torch.Tensor | None = None, weight_scale: float = 1.0) -> None:
     """Per row: the ``top`` experts with the largest fp32 logits ``w_router h + b_router`` (int32 [rows, top]), the
-    softmax over those logits alone (fp32 [rows, top]), and ``sigmoid(w_shared_gate . h)`` (fp32 [rows]) if asked."""
-    _cuda(chosen, weight, shared_gate, h, w_router, b_router, w_shared_gate)
+    softmax over those logits alone (fp32 [rows, top]), and ``sigmoid(w_shared_gate . h)`` (fp32 [rows]) if asked.
+    With ``score_all`` the scores are the softmax over every router output, the choice goes by score + ``correction``
+    (fp32 [outputs], may be None) and the weights are the chosen scores times ``weight_scale``, not renormalised."""
+    _cuda(chosen, weight, shared_gate, h, w_router, b_router, w_shared_gate, correction)
     experts, width = w_router.shape
+    _need(correction is None or (score_all and correction.dtype == torch.float32 and correction.numel() == experts
+                                 and correction.is_contiguous()), "moe_route: the correction is fp32 [router outputs] and goes with score_all")
     _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.is_contiguous() and weight.is_contiguous()
           and chosen.shape[1] == weight.shape[1] == top and chosen.shape[0] >= n_rows, "moe_route: chosen int32 / weight fp32 [rows, top]")
     _need(h.stride(1) == 1 and h.shape[1] == width and h.dtype == w_router.dtype and w_router.is_contiguous() and 0 < top <= experts,
@@ -1422,13 +1472,20 @@ def moe_route(chosen: torch.Tensor, weight: torch.Tensor, shared_gate: torch.Ten
         "moe_route: the shared gate needs a vector of the activations' type and an fp32 output")
     code = _fn("moe", "tw_moe_route")(_ptr(chosen), _ptr(weight), _ptr(shared_gate), _ptr(h), c_int(h.stride(0)), _ptr(w_router),
                                       _ptr(b_router), _ptr(w_shared_gate), c_int(n_rows), c_int(width), c_int(experts), c_int(top),
+                                      c_int(1 if score_all else 0), _ptr(correction), c_float(weight_scale),
                                       c_int(dtype_code(h.dtype)), _stream())
     _check(code, "moe_route")
 
 
-def moe_gate_up(act: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Tensor, chosen: torch.Tensor, n_rows: int) -> None:
+GLU_SILU, GLU_CLAMPED = 0, 1      # what an expert makes of its gate and up products (csrc/moe.cu: tw_glu)
+
+
+def moe_gate_up(act: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Tensor, chosen: torch.Tensor, n_rows: int,
+                glu: int = GLU_SILU, limit: float = 0.0, alpha: float = 1.0) -> None:
     """act[row, j] = silu(Wg_e h[row]) * (Wu_e h[row]) for the j-th chosen expert e of the row;
-    ``w_gate_up`` is [experts, 2, ff, width] (a gate matrix followed by its up matrix)."""
+    ``w_gate_up`` is [experts, 2, ff, width] (a gate matrix followed by its up matrix).  ``GLU_CLAMPED``: with
+    g = min(gate, limit) and u = clamp(up, -limit, limit) the activation is g * sigmoid(alpha g) * (u + 1).  A chosen
+    index beyond the experts (an expert without matrices) leaves its row of ``act`` untouched."""
     _cuda(act, h, w_gate_up, chosen)
     experts, two, ff, width = w_gate_up.shape
     top = chosen.shape[1]
@@ -1436,22 +1493,38 @@ def moe_gate_up(act: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Tensor, cho
           and act.is_contiguous() and tuple(act.shape[1:]) == (top, ff) and act.shape[0] >= n_rows, "moe_gate_up: bad operands")
     _need(h.dtype == torch.float32 or (w_gate_up.data_ptr() % 16 == 0), "moe_gate_up: weights must be 16-byte aligned")
     code = _fn("moe", "tw_moe_gate_up")(_ptr(act), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(chosen), c_int(n_rows), c_int(width),
-                                        c_int(ff), c_int(experts), c_int(top), c_int(dtype_code(h.dtype)), _stream())
+                                        c_int(ff), c_int(experts), c_int(top), c_int(glu), c_float(limit), c_float(alpha),
+                                        c_int(dtype_code(h.dtype)), _stream())
     _check(code, "moe_gate_up")
 
 
+def glu_rows(out: torch.Tensor, gate_up: torch.Tensor, n_rows: int, glu: int, limit: float = 0.0, alpha: float = 1.0) -> None:
+    """out[n, i] = glu(gate_up[n, i], gate_up[n, I + i]) over rows [all gates | all ups] (see ``moe_gate_up``)."""
+    _cuda(out, gate_up)
+    inter = out.shape[1]
+    _need(gate_up.shape[1] == 2 * inter and gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
+          and min(out.shape[0], gate_up.shape[0]) >= n_rows, "glu_rows: gate_up must be contiguous [n, 2I] of the output type")
+    code = _fn("moe", "tw_glu_rows")(_ptr(out), _ptr(gate_up), c_int(n_rows), c_int(inter), c_int(glu), c_float(limit),
+                                     c_float(alpha), c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "glu_rows")
+
+
 def moe_down(out: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-             shared: torch.Tensor | None, shared_gate: torch.Tensor | None, n_rows: int) -> None:
+             shared: torch.Tensor | None, shared_gate: torch.Tensor | None, n_rows: int,
+             h: torch.Tensor | None = None, identity: int = 0) -> None:
     """out[row] = sum_j weight[row, j] * Wd_e act[row, j]  (+ shared_gate[row] * shared[row]); ``w_down`` is
-    [experts, width, ff]."""
-    _cuda(out, act, w_down, chosen, weight, shared, shared_gate)
+    [experts, width, ff].  A chosen index in experts .. experts + ``identity`` - 1 adds weight * ``h[row]`` instead."""
+    _cuda(out, act, w_down, chosen, weight, shared, shared_gate, h)
+    _need(identity == 0 or (h is not None and h.stride(1) == 1 and h.dtype == out.dtype and h.shape[1] == out.shape[1]),
+          "moe_down: identity experts need the rows themselves")
     experts, width, ff = w_down.shape
     top = chosen.shape[1]
     _need(w_down.is_contiguous() and act.is_contiguous() and tuple(act.shape[1:]) == (top, ff) and out.is_contiguous()
           and out.shape[1] == width and out.dtype == act.dtype == w_down.dtype, "moe_down: bad operands")
     _need(shared is None or (shared.is_contiguous() and shared.dtype == out.dtype and shared.shape[1] == width), "moe_down: bad shared rows")
     code = _fn("moe", "tw_moe_down")(_ptr(out), _ptr(act), _ptr(w_down), _ptr(chosen), _ptr(weight), _ptr(shared), _ptr(shared_gate),
-                                     c_int(n_rows), c_int(width), c_int(ff), c_int(experts), c_int(top), c_int(dtype_code(out.dtype)), _stream())
+                                     c_int(n_rows), c_int(width), c_int(ff), c_int(experts), c_int(top), _ptr(h),
+                                     c_int(0 if h is None else h.stride(0)), c_int(identity), c_int(dtype_code(out.dtype)), _stream())
     _check(code, "moe_down")
 
 
@@ -1489,15 +1562,23 @@ def moe_gather(xs: torch.Tensor, h: torch.Tensor, order: torch.Tensor, pairs: in
 
 
 def moe_combine(out: torch.Tensor, ys: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, shared: torch.Tensor | None,
-                shared_gate: torch.Tensor | None, n_rows: int) -> None:
-    """out[row] = sum_j weight[row, j] * ys[place[row * top + j]]  (+ shared_gate[row] * shared[row])."""
-    _cuda(out, ys, place, weight, shared, shared_gate)
+                shared_gate: torch.Tensor | None, n_rows: int, chosen: torch.Tensor | None = None, h: torch.Tensor | None = None,
+                experts: int = 0, identity: int = 0) -> None:
+    """out[row] = sum_j weight[row, j] * ys[place[row * top + j]]  (+ shared_gate[row] * shared[row]).  With
+    ``identity`` a pair without a place whose chosen index lies in experts .. experts + identity - 1 adds
+    weight * ``h[row]``."""
+    _cuda(out, ys, place, weight, shared, shared_gate, chosen, h)
+    _need(identity == 0 or (h is not None and chosen is not None and h.stride(1) == 1 and h.dtype == out.dtype
+                            and h.shape[1] == out.shape[1] and chosen.dtype == torch.int32 and chosen.is_contiguous()),
+          "moe_combine: identity experts need the chosen indices and the rows themselves")
     top, width = weight.shape[1], out.shape[1]
     _need(out.is_contiguous() and ys.is_contiguous() and ys.dtype == out.dtype and ys.shape[1] == width and weight.is_contiguous()
           and weight.dtype == torch.float32 and place.dtype == torch.int32, "moe_combine: bad operands")
     _need(shared is None or (shared.is_contiguous() and shared.dtype == out.dtype and shared.shape[1] == width), "moe_combine: bad shared rows")
     code = _fn("moe", "tw_moe_combine")(_ptr(out), _ptr(ys), _ptr(place), _ptr(weight), _ptr(shared), _ptr(shared_gate),
-                                        c_int(n_rows), c_int(top), c_int(width), c_int(dtype_code(out.dtype)), _stream())
+                                        c_int(n_rows), c_int(top), c_int(width), _ptr(chosen), _ptr(h),
+                                        c_int(0 if h is None else h.stride(0)), c_int(experts), c_int(identity),
+                                        c_int(dtype_code(out.dtype)), _stream())
     _check(code, "moe_combine")
 
 

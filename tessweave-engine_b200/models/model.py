@@ -132,6 +132,7 @@ class Model:
             stream.fold(ctx, stream)         # a block kept several copies of the stream: back to the one residual
         if n_logit_rows > 0:
             y = ctx.workspace.get("model.final", (n_logit_rows, self.spec.hidden_size), self.runtime.dtype)
-            self.final_norm.apply(ctx, y, stream.resid, stream.pending, n_logit_rows, rows=logit_rows)
+            self.final_norm.apply(ctx, y, stream.resid, stream.pending, n_logit_rows, rows=logit_rows,
+                                  delta_scale=stream.pending_scale)
             self.head.forward(ctx, logits, y, n_logit_rows)
         return logits

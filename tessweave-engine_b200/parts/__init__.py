@@ -4,7 +4,7 @@ from .base import (Block, Embedding, FeedForward, FixedState, Head, Mixer, Norm,
                    PositionEncoding, ResidualStream, RotaryPlan, Runtime, SeveralNeeds, SeveralViews, SplitSum, StateView, StepContext,
                    WeightDecl, Workspace,
                    build_part, dense_delta, join_name, register_part, registered)
-from . import embedding, norms, positions, attention, sigmoid_attention, recurrent, combined, feedforward, block, heads  # noqa: F401  (register the built-in kinds)
+from . import embedding, norms, positions, attention, latent_attention, sigmoid_attention, recurrent, combined, feedforward, block, heads  # noqa: F401  (register the built-in kinds)
 
 __all__ = ["Block", "Embedding", "FeedForward", "FixedState", "Head", "Mixer", "Norm", "PagedKV", "PagedView", "Part",
            "PartSpec", "PositionEncoding", "ResidualStream", "RotaryPlan", "Runtime", "SeveralNeeds", "SeveralViews", "SplitSum",

@@ -301,13 +301,18 @@ class Norm(Part):
     accepts_split_sum = False
 
     def apply(self, ctx: "StepContext", out: torch.Tensor, resid: torch.Tensor, delta, n_rows: int,
-              rows: torch.Tensor | None = None) -> None:
+              rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> None:
+        """``delta_scale``: the delta is multiplied by it (in fp32) as it joins the stream; a norm that cannot do
+        that implements ``forward`` without the argument and is only ever asked for a scale of 1."""
         if not self.accepts_split_sum:
             delta = dense_delta(ctx, delta, out.dtype)
-        self.forward(ctx, out, resid, delta, n_rows, rows)
+        if delta_scale == 1.0:
+            self.forward(ctx, out, resid, delta, n_rows, rows)
+        else:
+            self.forward(ctx, out, resid, delta, n_rows, rows, delta_scale=delta_scale)
 
     def forward(self, ctx: "StepContext", out: torch.Tensor, resid: torch.Tensor, delta, n_rows: int,
-                rows: torch.Tensor | None = None) -> None:
+                rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> None:
         raise NotImplementedError
 
     def add_normed(self, ctx: "StepContext", resid: torch.Tensor, delta, n_rows: int,
@@ -389,12 +394,23 @@ class ResidualStream:
     them last made that copy; whoever changes ``resid`` without renewing it sets it to None.
     ``copies``: fp32 [rows, copies, width] when a block keeps several parallel copies of the stream instead of
     ``resid``; such a block also sets ``fold``, which the model calls once behind the last block (and anyone who
-    wants the single stream in between) to bring ``resid`` up to date: ``fold(ctx, stream)``."""
+    wants the single stream in between) to bring ``resid`` up to date: ``fold(ctx, stream)``.
+    ``pending_scale``: what the pending delta is multiplied by when it is added (a design whose sub-layers join the
+    stream through a constant factor); whoever takes ``pending`` honours it or refuses (``unscaled_pending``)."""
     resid: torch.Tensor
     pending: object = None
+    pending_scale: float = 1.0
     rounded: torch.Tensor | None = None
     copies: torch.Tensor | None = None
     fold: Callable | None = None
+
+
+def unscaled_pending(stream: ResidualStream, who: str):
+    """The pending delta, for a block that adds it as it is; raises where the block before left one with a factor."""
+    if stream.pending is not None and stream.pending_scale != 1.0:
+        raise RuntimeError(f"{who}: the block before left a delta with the factor {stream.pending_scale}, which only a "
+                           "block that knows such factors can add")
+    return stream.pending
 
 
 # ---------------------------------------------------------------------------

@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import ops
 from .base import (Block, PartSpec, ResidualStream, Runtime, StepContext, WeightDecl, build_part, dense_delta, join_name,
-                   register_part)
+                   register_part, unscaled_pending)
 
 
 class ArrangedBlock(Block):
@@ -45,14 +45,16 @@ class PreNormBlock(ArrangedBlock):
     Reference: flow_engine/model.py:179-202.  The residual stream is fp32; each
     sub-layer's output is handed to the next norm as a pending delta, so the add
     and the norm are one kernel.  ``names`` gives the checkpoint's prefix of each
-    sub-part inside the layer.
+    sub-part inside the layer.  ``residual_scale`` m: x = x + m * sublayer(norm(x)) for both sub-layers; the product
+    is formed in fp32 by the kernel that adds the delta.
     """
 
     def __init__(self, runtime: Runtime, hidden: int, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec | None = None,
-                 feed_forward: PartSpec | None = None, names: dict[str, str] | None = None):
+                 feed_forward: PartSpec | None = None, names: dict[str, str] | None = None, residual_scale: float = 1.0):
         super().__init__(runtime, hidden, names)
         if (norm2 is None) != (feed_forward is None):
             raise ValueError("pre_norm block: norm2 and feed_forward come together or not at all")
+        self.residual_scale = float(residual_scale)
         self.norm1 = build_part("norm", norm1, runtime)
         self.mixer = build_part("mixer", mixer, runtime)
         self.norm2 = build_part("norm", norm2, runtime) if norm2 is not None else None
@@ -63,14 +65,15 @@ class PreNormBlock(ArrangedBlock):
         n = ctx.n_tokens
         stream.rounded = None
         h = ctx.workspace.get("block.h", (n, self.hidden), self.runtime.dtype)
-        self.norm1.apply(ctx, h, stream.resid, stream.pending, n)
+        self.norm1.apply(ctx, h, stream.resid, stream.pending, n, delta_scale=stream.pending_scale)
         ctx.upcoming_weights = self.feed_forward.streamed_first() if self.feed_forward is not None else None
         delta = self.mixer.forward(ctx, h, cache, write_cache)
         ctx.upcoming_weights = None
+        stream.pending_scale = self.residual_scale
         if self.feed_forward is None:
             stream.pending = delta                              # a layer of its first half only
             return
-        self.norm2.apply(ctx, h, stream.resid, delta, n)
+        self.norm2.apply(ctx, h, stream.resid, delta, n, delta_scale=self.residual_scale)
         stream.pending = self.feed_forward.forward(ctx, h)      # whoever normalises next adds it
 
 
@@ -109,6 +112,7 @@ class OutputNormBlock(ArrangedBlock):
         n = ctx.n_tokens
         if stream.pending is not None:
             raise RuntimeError("output_norm block: the block before left a delta that only a norm of its own kind can add")
+        stream.pending_scale = 1.0
         h, copy = self._rows(ctx, stream)
         ctx.upcoming_weights = self.feed_forward.streamed_first() if self.feed_forward is not None else None
         delta = self.mixer.forward(ctx, h, cache, write_cache)
@@ -181,7 +185,7 @@ class HyperPreNormBlock(ArrangedBlock):
             stream.copies = ctx.workspace.get("model.copies", (n, self.copies, self.hidden), torch.float32)
             stream.fold = self._fold
             args["init"] = stream.resid
-        elif stream.pending is not None:
+        elif unscaled_pending(stream, "hyper_pre_norm block") is not None:
             y, mix, out = stream.pending
             args.update(y=y, mix=mix, out_coef=out)
         stream.pending = None
@@ -239,7 +243,8 @@ class ParallelPreNormBlock(ArrangedBlock):
         n, dt = ctx.n_tokens, self.runtime.dtype
         stream.rounded = None
         h = ctx.workspace.get("block.h", (n, self.hidden), dt)
-        self.norm1.apply(ctx, h, stream.resid, stream.pending, n)
+        self.norm1.apply(ctx, h, stream.resid, stream.pending, n, delta_scale=stream.pending_scale)
+        stream.pending_scale = 1.0
         ctx.upcoming_weights = self.feed_forward.streamed_first() if self.feed_forward is not None else None
         delta = self.mixer.forward(ctx, h, cache, write_cache)
         ctx.upcoming_weights = None

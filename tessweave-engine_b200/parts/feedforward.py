@@ -101,23 +101,42 @@ class RoutedExperts(FeedForward):
     the pairs by expert and run every expert's rows through one library product, whose group bounds stay on the device.
     Steps of one row, float32 steps and odd sizes run each (token, expert) pair as matrix-vector products that stream
     the chosen experts' matrices (csrc/moe.cu).
+
+    Options of other designs.  ``score_all``: the scores are s = softmax(z) over *every* router output, the ``top``
+    outputs with the largest s + ``correction`` (a stored fp32 vector named by ``correction``, or none) are chosen, and
+    the weights are their s times ``weight_scale``, not renormalised.  ``identity`` n: the router has n outputs more
+    than there are experts; such an output is an expert without tensors whose result is the token's row itself.
+    ``activation``: ``{"kind": "clamped", "limit": l, "alpha": a}`` makes an expert's inner rows
+    g sigmoid(a g) (u + 1) with g = min(Wg h, l), u = clamp(Wu h, -l, l) instead of silu(Wg h) (Wu h).
     """
 
     GROUPED_MIN_ROWS = 1       # measured at 7B and 1.5B layer sizes: the sorted way is the faster one from two or three rows on
 
     def __init__(self, runtime: Runtime, hidden: int, experts: int, top: int, intermediate: int,
                  shared: PartSpec | None = None, shared_gate: bool = False, router_bias: bool = True,
-                 names: dict[str, str] | None = None):
+                 names: dict[str, str] | None = None, score_all: bool = False, correction: str | None = None,
+                 weight_scale: float = 1.0, identity: int = 0, activation: dict | None = None):
         super().__init__(runtime)
-        if min(hidden, experts, top, intermediate) <= 0 or top > experts:
-            raise ValueError("routed_experts: sizes must be positive and top at most the number of experts")
+        if min(hidden, experts, top, intermediate) <= 0 or identity < 0 or top > experts + identity:
+            raise ValueError("routed_experts: sizes must be positive and top at most the number of router outputs")
         if shared_gate and shared is None:
             raise ValueError("routed_experts: a gate of the shared expert needs a shared expert")
+        if (correction is not None or weight_scale != 1.0) and not score_all:
+            raise ValueError("routed_experts: a correction of the choice and a scale of the weights go with score_all")
         self.hidden, self.experts, self.top, self.intermediate = hidden, experts, top, intermediate
+        self.identity, self.outputs = int(identity), experts + int(identity)
+        self.score_all, self.weight_scale = bool(score_all), float(weight_scale)
+        self.glu, self.glu_limit, self.glu_alpha = ops.GLU_SILU, 0.0, 1.0
+        if activation is not None:
+            if activation.get("kind") != "clamped" or not float(activation["limit"]) > 0:
+                raise ValueError(f"routed_experts: unknown activation {activation!r} (known: clamped with a positive limit)")
+            self.glu, self.glu_limit, self.glu_alpha = ops.GLU_CLAMPED, float(activation["limit"]), float(activation.get("alpha", 1.0))
         self.names = {"router": "router", "router_bias": "router.b", "expert": "e", "gate": "gate", "up": "up", "down": "down",
                       "shared": "shared", "shared_gate": "shared.sg", **(names or {})}
-        self.w_router = runtime.empty(experts, hidden)
-        self.b_router = runtime.empty(experts, dtype=torch.float32) if router_bias else None
+        self.w_router = runtime.empty(self.outputs, hidden)
+        self.b_router = runtime.empty(self.outputs, dtype=torch.float32) if router_bias else None
+        self.correction_name = correction
+        self.correction = runtime.empty(self.outputs, dtype=torch.float32) if correction is not None else None
         self.w_gate_up = runtime.empty(experts, 2, intermediate, hidden)
         self.w_down = runtime.empty(experts, hidden, intermediate)
         self.shared = build_part("feed_forward", shared, runtime) if shared is not None else None
@@ -126,9 +145,11 @@ class RoutedExperts(FeedForward):
 
     def weights(self) -> list[WeightDecl]:
         nm, f, hid = self.names, self.intermediate, self.hidden
-        decls = [WeightDecl(nm["router"], (self.experts, hid), dest=self.w_router)]
+        decls = [WeightDecl(nm["router"], (self.outputs, hid), dest=self.w_router)]
         if self.b_router is not None:
-            decls.append(WeightDecl(nm["router_bias"], (self.experts,), role="vector", dest=self.b_router))
+            decls.append(WeightDecl(nm["router_bias"], (self.outputs,), role="vector", dest=self.b_router))
+        if self.correction is not None:
+            decls.append(WeightDecl(self.correction_name, (self.outputs,), role="vector", init="wide_normal", dest=self.correction))
         for e in range(self.experts):
             p = f"{nm['expert']}{e}"
             decls += [WeightDecl(join_name(p, nm["gate"]), (f, hid), dest=self.w_gate_up[e, 0]),
@@ -154,7 +175,8 @@ class RoutedExperts(FeedForward):
         weight = ws.get("moe.weight", (n, self.top), torch.float32)
         gate = ws.get("moe.shared_gate", (n,), torch.float32) if self.w_shared_gate is not None else None
         ops.moe_route(chosen, weight, gate, h, self.w_router, self.b_router,
-                      self.w_shared_gate.view(-1) if self.w_shared_gate is not None else None, n, self.top)
+                      self.w_shared_gate.view(-1) if self.w_shared_gate is not None else None, n, self.top,
+                      score_all=self.score_all, correction=self.correction, weight_scale=self.weight_scale)
         return chosen, weight, gate
 
     def forward(self, ctx: StepContext, h: torch.Tensor):
@@ -171,8 +193,8 @@ class RoutedExperts(FeedForward):
             # (a library without a grouped product reads the group bounds on the host: not inside a captured step)
             self._grouped(ctx, h, chosen, weight, shared, gate, out, sorted_buffers)
             return out
-        ops.moe_gate_up(act, h, self.w_gate_up, chosen, n)
-        ops.moe_down(out, act, self.w_down, chosen, weight, shared, gate, n)
+        ops.moe_gate_up(act, h, self.w_gate_up, chosen, n, glu=self.glu, limit=self.glu_limit, alpha=self.glu_alpha)
+        ops.moe_down(out, act, self.w_down, chosen, weight, shared, gate, n, h=h if self.identity else None, identity=self.identity)
         return out
 
     def grouped_for(self, n_rows: int) -> bool:
@@ -197,6 +219,12 @@ class RoutedExperts(FeedForward):
         ops.moe_sort(order, place, ends, chosen, n)
         ops.moe_gather(xs, h, order, pairs, self.top)
         gate_up = grouped_matmul_nt(xs, self.w_gate_up.view(self.experts, 2 * self.intermediate, self.hidden), ends)
-        ops.silu_mul(act, gate_up, pairs, False)
+        if self.glu == ops.GLU_SILU:
+            ops.silu_mul(act, gate_up, pairs, False)
+        else:
+            ops.glu_rows(act, gate_up, pairs, self.glu, self.glu_limit, self.glu_alpha)
         ys = grouped_matmul_nt(act, self.w_down, ends)
-        ops.moe_combine(out, ys, place, weight, shared, gate, n)
+        if self.identity:
+            ops.moe_combine(out, ys, place, weight, shared, gate, n, chosen=chosen, h=h, experts=self.experts, identity=self.identity)
+        else:
+            ops.moe_combine(out, ys, place, weight, shared, gate, n)

@@ -14,11 +14,16 @@ class LinearHead(Head):
 
     With ``tied`` the matrix is the embedding's: one buffer, two users, and the checkpoint brings no
     tensor for the head (flow_engine/model.py:110-112).  Steps with few rows stream the matrix once
-    through the hand-written kernels; the rest is a library product.
+    through the hand-written kernels; the rest is a library product.  ``softcap`` c: the logits are then bent into
+    (-c, c), logits <- c tanh(logits / c), in fp32.
     """
 
-    def __init__(self, runtime: Runtime, vocab: int, hidden: int, tied: torch.Tensor | None = None, weight_name: str = "weight"):
+    def __init__(self, runtime: Runtime, vocab: int, hidden: int, tied: torch.Tensor | None = None, weight_name: str = "weight",
+                 softcap: float | None = None):
         super().__init__(runtime)
+        if softcap is not None and not softcap > 0:
+            raise ValueError("head: the cap of the logits must be positive")
+        self.softcap = float(softcap) if softcap is not None else None
         if min(vocab, hidden) <= 0:
             raise ValueError("head needs a positive vocabulary and width")
         self.vocab, self.hidden = int(vocab), int(hidden)
@@ -42,3 +47,5 @@ class LinearHead(Head):
             ops.gemm_small_m(out, y, self.weight, n_rows)
         else:
             matmul_nt(out, y[:n_rows], self.weight)
+        if self.softcap is not None:
+            ops.softcap(out, self.softcap)

@@ -37,8 +37,8 @@ class RMSNorm(Norm):
         if self.unit_offset:
             torch.add(self._stored, 1.0, out=self.weight)
 
-    def forward(self, ctx: StepContext, out, resid, delta, n_rows, rows=None) -> None:
-        ops.add_rmsnorm(out, resid, delta, self.weight, self.eps, n_rows, rows)
+    def forward(self, ctx: StepContext, out, resid, delta, n_rows, rows=None, delta_scale: float = 1.0) -> None:
+        ops.add_rmsnorm(out, resid, delta, self.weight, self.eps, n_rows, rows, delta_scale=delta_scale)
 
     def add_normed(self, ctx: StepContext, resid, delta, n_rows, copy=None) -> None:
         ops.rmsnorm_to_residual(resid, delta, self.weight, self.eps, n_rows, copy)

@@ -9,6 +9,32 @@ from ..csrc import ops
 from .base import PositionEncoding, RotaryPlan, Runtime, StepContext, register_part
 
 
+def stretched_frequencies(theta: float, dims: int, yarn: dict) -> list[float]:
+    """The turning rate of every pair under the YaRN rule (see ``RotaryEmbedding``), in double precision."""
+
+    def pair_turning(t: float) -> float:        # the (fractional) pair that makes t turns over the original length
+        return dims * math.log(yarn["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_turning(yarn["fast"])), 0)
+    hi = min(math.ceil(pair_turning(yarn["slow"])), dims - 1)
+    out = []
+    for i in range(dims // 2):
+        f = theta ** (-2.0 * i / dims)
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / yarn["factor"] * ramp + f * (1.0 - ramp))
+    return out
+
+
+def checked_yarn(yarn: dict | None, theta: float) -> tuple[dict | None, float]:
+    """(the four numbers as floats, the factor on cos and sin) of a ``yarn`` parameter; (None, 1) without one."""
+    if yarn is None:
+        return None, 1.0
+    y = {k: float(yarn[k]) for k in ("factor", "original", "fast", "slow")}
+    if min(y.values()) <= 0 or not theta > 1:
+        raise ValueError("rope: yarn needs positive factor, original, fast and slow, and theta above 1")
+    return y, 0.1 * math.log(y["factor"]) + 1.0
+
+
 @register_part("position", "rope")
 class RotaryEmbedding(PositionEncoding):
     """Rotate-half rotary encoding over the whole head, or over its first ``dims`` values.
@@ -29,13 +55,7 @@ class RotaryEmbedding(PositionEncoding):
 
     def __init__(self, runtime: Runtime, theta: float, dims: int | None = None, yarn: dict | None = None):
         super().__init__(runtime)
-        self.yarn = None
-        self.magnitude = 1.0
-        if yarn is not None:
-            self.yarn = {k: float(yarn[k]) for k in ("factor", "original", "fast", "slow")}
-            if min(self.yarn.values()) <= 0 or not theta > 1:
-                raise ValueError("rope: yarn needs positive factor, original, fast and slow, and theta above 1")
-            self.magnitude = 0.1 * math.log(self.yarn["factor"]) + 1.0
+        self.yarn, self.magnitude = checked_yarn(yarn, theta)
         if not theta > 0:
             raise ValueError("rope theta must be positive")
         if dims is not None and (dims < 0 or dims % 2):
@@ -57,19 +77,7 @@ class RotaryEmbedding(PositionEncoding):
         return table
 
     def _yarn_frequencies(self, dims: int) -> list[float]:
-        y = self.yarn
-
-        def pair_turning(t: float) -> float:        # the (fractional) pair that makes t turns over the original length
-            return dims * math.log(y["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
-
-        lo = max(math.floor(pair_turning(y["fast"])), 0)
-        hi = min(math.ceil(pair_turning(y["slow"])), dims - 1)
-        out = []
-        for i in range(dims // 2):
-            f = self.theta ** (-2.0 * i / dims)
-            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
-            out.append(f / y["factor"] * ramp + f * (1.0 - ramp))
-        return out
+        return stretched_frequencies(self.theta, dims, self.yarn)
 
     def _dims(self, head_dim: int) -> int:
         dims = head_dim if self.dims is None else self.dims
@@ -104,11 +112,13 @@ class InterleavedRotaryEmbedding(PositionEncoding):
         f_i = theta ** (-(2 i) / dims),  a = float(position) * f_i,  i < dims / 2
         (x[2i], x[2i+1]) -> (x[2i] cos a - x[2i+1] sin a,  x[2i+1] cos a + x[2i] sin a)
 
-    all in fp32.  The table of f_i is made once per head size on the host.
+    all in fp32.  The table of f_i is made once per head size on the host.  ``yarn`` as for ``rope``: stretched
+    rates per pair, and cos and sin both multiplied by 0.1 ln(factor) + 1.
     """
 
-    def __init__(self, runtime: Runtime, theta: float, dims: int | None = None):
+    def __init__(self, runtime: Runtime, theta: float, dims: int | None = None, yarn: dict | None = None):
         super().__init__(runtime)
+        self.yarn, self.magnitude = checked_yarn(yarn, theta)
         if not theta > 0:
             raise ValueError("rope theta must be positive")
         if dims is not None and (dims < 0 or dims % 2):
@@ -122,15 +132,18 @@ class InterleavedRotaryEmbedding(PositionEncoding):
             dims = head_dim if self.dims is None else self.dims
             if dims > head_dim or dims % 2:
                 raise ValueError(f"rope over {dims} dims does not fit a head of {head_dim}")
-            inv = self.theta ** (-torch.arange(0, dims, 2, dtype=torch.float32) / max(dims, 1))
-            plan = RotaryPlan(inv.to(self.runtime.device), dims, interleaved=True)
+            if self.yarn is None:
+                inv = self.theta ** (-torch.arange(0, dims, 2, dtype=torch.float32) / max(dims, 1))
+            else:
+                inv = torch.tensor(stretched_frequencies(self.theta, dims, self.yarn), dtype=torch.float64).to(torch.float32)
+            plan = RotaryPlan(inv.to(self.runtime.device), dims, interleaved=True, magnitude=self.magnitude)
             self._plans[head_dim] = plan
         return plan
 
     def apply(self, ctx: StepContext, qk: torch.Tensor, n_heads: int, head_dim: int) -> None:
         plan = self.rotary_plan(head_dim)
         ops.rotate_pairs(qk, ctx.positions, ctx.seq_of_token, plan.inv_freq, ctx.n_tokens, n_heads, head_dim,
-                         plan.rot_dims, plan.interleaved)
+                         plan.rot_dims, plan.interleaved, magnitude=plan.magnitude)
 
 
 @register_part("position", "none")

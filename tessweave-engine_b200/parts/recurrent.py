@@ -395,3 +395,61 @@ class GatedDelta(MatrixStateMixer):
                              p0=self.rate_log, p1=self.dt_bias, write_pre=small, channel_decay=self.channel_decay,
                              qk_group=H // self.n_qk_heads)
         return self._finish(ctx, raw, None, self.norm_per_head, gate)
+
+
+@register_part("mixer", "gla")
+class GatedLinearAttention(MatrixStateMixer):
+    """Linear attention whose state forgets through one gate per key channel that the token sets.
+
+        q, k, v, g = split(h W^T);  q <- q * key_dim^-1/2              rows [Wq; Wk; Wv; Wg]
+        z = Wa2 (Wa1 h) + b                                            per head and key channel, fp32 (inner size ``decay_rank``)
+        a = sigmoid(z)^(1 / tau)                                       evaluated as exp(logsigmoid(z) / tau), fp32
+        S_t = diag(a_t) S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t         fp32, S zero before the first token
+        delta = (rms_head(o) * norm * silu(g)) Wo^T                    norm [value_dim] serves every head
+
+    ``names``: q, k, v, gate, out, norm, a1, a2, a2_bias.
+    """
+
+    rule = ops.RECURRENCE_GLA
+    gate_act = ops.GATE_SILU
+    NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "norm": "norm", "a1": "a1", "a2": "a2", "a2_bias": "a2.b"}
+
+    def __init__(self, runtime: Runtime, hidden: int, n_heads: int, key_dim: int, value_dim: int, decay_rank: int, tau: float,
+                 eps: float, names: dict[str, str] | None = None):
+        super().__init__(runtime)
+        self._sizes(hidden, n_heads, key_dim, value_dim, eps)
+        if decay_rank <= 0 or not tau > 0:
+            raise ValueError("gla: decay_rank and tau must be positive")
+        self.decay_rank, self.tau = int(decay_rank), float(tau)
+        self.names = {**self.NAMES, **(names or {})}
+        self.w_in = runtime.empty(2 * self.qk_size + 2 * self.v_size, hidden)          # rows [Wq; Wk; Wv; Wg]
+        self.w_a1 = runtime.empty(self.decay_rank, hidden)
+        self.w_a2 = runtime.empty(self.qk_size, self.decay_rank)
+        self.b_a2 = runtime.empty(self.qk_size, dtype=torch.float32)
+        self.norm = runtime.empty(value_dim, dtype=torch.float32)
+        self.norm_per_head = runtime.empty(self.v_size, dtype=torch.float32)
+        self.w_o = runtime.empty(hidden, self.v_size)
+
+    def weights(self) -> list[WeightDecl]:
+        a, b, nm, hid = self.qk_size, self.v_size, self.names, self.hidden
+        return [WeightDecl(nm["q"], (a, hid), dest=self.w_in[:a]),
+                WeightDecl(nm["k"], (a, hid), dest=self.w_in[a:2 * a]),
+                WeightDecl(nm["v"], (b, hid), dest=self.w_in[2 * a:2 * a + b]),
+                WeightDecl(nm["gate"], (b, hid), dest=self.w_in[2 * a + b:]),
+                WeightDecl(nm["a1"], (self.decay_rank, hid), dest=self.w_a1),
+                WeightDecl(nm["a2"], (a, self.decay_rank), dest=self.w_a2),
+                WeightDecl(nm["a2_bias"], (a,), role="vector", init="wide_normal", dest=self.b_a2),
+                WeightDecl(nm["norm"], (self.value_dim,), role="vector", init="one_plus_normal", dest=self.norm),
+                WeightDecl(nm["out"], (hid, b), dest=self.w_o)]
+
+    def finalize(self) -> None:
+        self.norm_per_head.view(self.n_heads, self.value_dim).copy_(self.norm.expand(self.n_heads, self.value_dim))
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
+        cache = self._check(cache)
+        a, b = self.qk_size, self.v_size
+        proj = linear(ctx, "gla.in", h, self.w_in)
+        decay = linear(ctx, "gla.a2", linear(ctx, "gla.a1", h, self.w_a1), self.w_a2, out_dtype=torch.float32)
+        raw, _ = self._recur(ctx, proj[:, :a], proj[:, a:2 * a], proj[:, 2 * a:2 * a + b], cache, write_cache,
+                             pre=decay, p0=self.b_a2, q_scale=self.key_dim ** -0.5, cap=1.0 / self.tau)
+        return self._finish(ctx, raw, None, self.norm_per_head, proj[:, 2 * a + b:])
