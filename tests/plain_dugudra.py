@@ -11,7 +11,6 @@ from pathlib import Path
 import torch
 
 
-
 # ---------------------------------------------------------------------------
 # small pieces
 # ---------------------------------------------------------------------------
@@ -191,12 +190,11 @@ def mixture(h, w, p, mlp):
 # ---------------------------------------------------------------------------
 def forward(cfg, w, tokens, return_layers=False):
     """logits [T, vocab] of one sequence (and the residual rows behind every layer)."""
-    dtype = w["embed"].dtype
     eps = cfg["norm"]["eps"]
-    mult = cfg["residual_mult"]
+    mult = cfg.get("residual_mult", 1.0)
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(len(tokens))
-    x = w["embed"][tokens] * cfg["embedding"]["scale"]
+    x = w["embed"][tokens] * (cfg.get("embedding") or {}).get("scale", 1.0)
     layers = []
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -211,7 +209,6 @@ def forward(cfg, w, tokens, return_layers=False):
     cap = cfg.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
-    del dtype
     return (logits, torch.stack(layers)) if return_layers else logits
 
 

@@ -241,3 +241,53 @@ def test_generate_nufatar_as_a_user_starts_it(tmp_path):
     assert proc.returncode == 0, proc.stderr[-3000:]
     got = [int(t) for t in proc.stdout.strip().split(",")]
     assert got == plain_nufatar.greedy(folder, prompt, 8)
+
+
+# ---------------------------------------------------------------------------
+# the Dugudra decoder through the same command line
+# ---------------------------------------------------------------------------
+def test_doctor_and_inspect_know_dugudra(tmp_path):
+    from tiny_dugudra import DUGUDRA_A
+    assert "Dugudra" in json.loads(run_cli("doctor").stdout)["architectures"]
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(DUGUDRA_A))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 2, "--init-std", 0.1).returncode == 0
+    proc = run_cli("inspect", folder, "--kv-blocks", 10, "--block-size", 8)
+    assert proc.returncode == 0, proc.stderr
+    out = json.loads(proc.stdout)
+    per_token = states = 0
+    for layer in DUGUDRA_A["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            per_token += m["kv_heads"] * (m["dim"] + m["vdim"])
+        elif layer["type"] == "latent_attention":
+            per_token += m["kv_rank"] + m["rot_dim"]            # one row per token serves as key and value
+        else:
+            states += m["heads"] * m["dim"] * m["vdim"]
+    assert out["layers_in_schedule"] == len(DUGUDRA_A["layers"])
+    assert out["kv_bf16_bytes"] == per_token * 2 * 10 * 8
+    assert out["state_bytes_per_request"] == 4 * states
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps({**DUGUDRA_A, "layers": [{**DUGUDRA_A["layers"][0], "type": "conv"}]}))
+    proc = run_cli("inspect", bad)
+    assert proc.returncode != 0 and "not implemented" in proc.stderr
+
+
+@pytest.mark.gpu
+def test_generate_dugudra_as_a_user_starts_it(tmp_path):
+    """init -> generate --prompt-ids in float32 -> the plain implementation's greedy continuation."""
+    import plain_dugudra
+    from tiny_dugudra import DUGUDRA_D
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(DUGUDRA_D))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 11, "--init-std", 0.25).returncode == 0
+    prompt = [5, 17, 3, 20, 41, 7, 50, 10, 23]
+    proc = run_cli("generate", folder, "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32", "--max-tokens", 8,
+                   "--ignore-eos", "--log", tmp_path / "runs" / "engine.jsonl", "--block-size", 8, "--kv-blocks", 32,
+                   "--prefill-chunk", 4, "--max-context", 256)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    got = [int(t) for t in proc.stdout.strip().split(",")]
+    assert got == plain_dugudra.greedy(folder, prompt, 8)
