@@ -7,6 +7,7 @@ decode through the Python entry point, prefill of 2,048 tokens, and decode at ba
     python bench.py --design linurax          # the Linurax decoder beside Qwen2 at equal layer sizes (a record of its own)
     python bench.py --design sapatar          # the same for the Sapatar decoder
     python bench.py --design nufatar          # the same for the Nufatar decoder (beside Sapatar and Qwen2)
+    python bench.py --design dugudra          # the same for the Dugudra decoder (beside Sapatar and Qwen2)
 
 The default run has the layer sizes of the Qwen2.5-7B-sized benchmark configuration with
 random weights (N(0, 0.02), drawn on the device), a batch of 8 and a context of 4,096 tokens.
@@ -354,7 +355,7 @@ def workload_run(name: str, layers: int | None) -> dict:
 
 
 def design_run(args, pk: dict, pk_source: str) -> dict:
-    """``--design linurax|sapatar|nufatar``: that decoder and the Qwen2 decoder at the layer sizes of the benchmark
+    """``--design linurax|sapatar|nufatar|dugudra``: that decoder and the Qwen2 decoder at the layer sizes of the benchmark
     configuration (``--layers`` of them, default 8 here), random weights: a prompt step of 2,048 tokens, decode at
     batch 1 and ``--batch`` with ``--context`` keys, and the design's own kernels alone."""
     import torch
@@ -366,11 +367,12 @@ def design_run(args, pk: dict, pk_source: str) -> dict:
     record = {"design": args.design, "layers": layers, "batch": args.batch, "context": args.context,
               "prefill_tokens": PREFILL_TOKENS, "peaks": pk, "peaks_source": pk_source, "dtype": "bf16",
               "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
-    like = {"linurax": db.linurax_config_like, "sapatar": db.sapatar_config_like, "nufatar": db.nufatar_config_like}[args.design]
+    like = {"linurax": db.linurax_config_like, "sapatar": db.sapatar_config_like, "nufatar": db.nufatar_config_like,
+            "dugudra": db.dugudra_config_like}[args.design]
     for name, qwen in sizes.items():
         entry = {}
         beside = [("qwen2", dict(qwen, num_hidden_layers=layers))]
-        if args.design == "nufatar":      # the closest design in the tree: attention beside a matrix memory
+        if args.design in ("nufatar", "dugudra"):      # the closest design in the tree: windowed attention, matrix memories, experts
             beside.insert(0, ("sapatar", db.sapatar_config_like(qwen, layers)))
         for design, config in [(args.design, like(qwen, layers))] + beside:
             model = db.build(config)
@@ -384,6 +386,11 @@ def design_run(args, pk: dict, pk_source: str) -> dict:
     if args.design == "linurax":
         _, spec = tw.resolve(db.linurax_config_like(BENCH_CONFIG, 4))
         rows = db.linurax_kernel_table(spec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
+    elif args.design == "dugudra":
+        rows = db.dugudra_kernel_table(db.dugudra_config_like(BENCH_CONFIG, 4), args.batch, args.context, PREFILL_TOKENS,
+                                       pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
+        rows += db.sapatar_kernel_table(db.sapatar_config_like(BENCH_CONFIG, 4), args.batch, args.context, PREFILL_TOKENS,
+                                        pk["hbm_gbs"], pk["bf16_tflops"])
     elif args.design == "nufatar":
         rows = db.nufatar_kernel_table(db.nufatar_config_like(BENCH_CONFIG, 4), args.batch, args.context, PREFILL_TOKENS,
                                        pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
@@ -489,7 +496,7 @@ def main() -> int:
     ap.add_argument("--timeline", action="store_true",
                     help="record one decode step block by block on the device (kernels compiled with their recorder) "
                          "and print its launches in time order; for looking at, not a measurement")
-    ap.add_argument("--design", choices=["linurax", "sapatar", "nufatar"], default=None,
+    ap.add_argument("--design", choices=["linurax", "sapatar", "nufatar", "dugudra"], default=None,
                     help="another design beside the Qwen2 decoder at equal layer sizes: prompt and decode throughput of "
                          "both, and the design's own kernels with their rooflines (a record of its own; the default "
                          "workload and its JSON line are not touched)")

@@ -21,7 +21,7 @@ from .linurax_config import _finite, _need, _positive_int
 from .model_config import ConfigError
 from .sapatar_config import safetensors_shapes
 
-MAX_HEAD = 256          # the attention kernels' largest head
+MAX_HEAD = 1024         # the attention kernels' largest head (above 256: the exact kernel alone)
 
 
 def _window(d: dict, where: str) -> int | None:

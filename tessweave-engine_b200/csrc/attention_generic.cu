@@ -1,7 +1,7 @@
 // Paged causal attention for any mix of rows: one block per (token, query head).
 //
 // This is the exact-arithmetic kernel: fp32 scores, fp32 online softmax, fp32
-// accumulation, any head size up to 256 (keys and values may differ in size:
+// accumulation, any head size up to 1024 (keys and values may differ in size:
 // D for queries and keys, Dv for values and the output), any number of heads
 // and groups, an optional window.  It serves the whole float32 path and any bfloat16 shape
 // that the tensor-core kernels refuse.  Prompt portions and single decoded
@@ -21,9 +21,9 @@
 #include "common.cuh"
 
 #define TW_ATTN_WARPS 4
-#define TW_ATTN_MAXR 8  // head_dim <= 32 * 8
+// values of a head that a lane keeps in registers: 8 serves heads up to 256, 32 heads up to 1024
 
-template <typename T>
+template <typename T, int TW_ATTN_MAXR>
 __global__ void attn_generic_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q, int q_stride,
                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                     const int* __restrict__ seq_slot, const int* __restrict__ block_table,
@@ -121,18 +121,22 @@ TW_EXPORT int tw_attn_generic(void* out, int out_stride, const void* q, int q_st
                               int bias_rows, const float* sink, int dtype, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dist_bias && bias_rows <= 0) return (int)cudaErrorInvalidValue;
-    if (D <= 0 || D > 32 * TW_ATTN_MAXR || Dv <= 0 || Dv > 32 * TW_ATTN_MAXR || Hkv <= 0 || Hq % Hkv) return (int)cudaErrorInvalidValue;
+    if (D <= 0 || D > 1024 || Dv <= 0 || Dv > 1024 || Hkv <= 0 || Hq % Hkv) return (int)cudaErrorInvalidValue;
     dim3 grid(n_tokens, Hq);
     const size_t smem = (size_t)TW_ATTN_WARPS * (Dv + 2) * sizeof(float);
-    if (dtype == TW_F32)
-        tw_launch(attn_generic_kernel<float>, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1, 
+    const bool wide = D > 256 || Dv > 256;
+    if (dtype == TW_F32) {
+        auto kernel = wide ? attn_generic_kernel<float, 32> : attn_generic_kernel<float, 8>;
+        tw_launch(kernel, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1,
             (float*)out, out_stride, (const float*)q, q_stride, positions, seq_of_token, seq_slot, block_table,
             table_stride, (const float*)k_cache, (const float*)v_cache, Hq, Hkv, D, Dv, page_size, num_pages, window, scale,
             dist_bias, bias_rows, sink, status);
-    else
-        tw_launch(attn_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1, 
+    } else {
+        auto kernel = wide ? attn_generic_kernel<__nv_bfloat16, 32> : attn_generic_kernel<__nv_bfloat16, 8>;
+        tw_launch(kernel, dim3(grid), dim3(32 * TW_ATTN_WARPS), smem, stream, 1,
             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, positions, seq_of_token, seq_slot,
             block_table, table_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, Hq, Hkv, D, Dv,
             page_size, num_pages, window, scale, dist_bias, bias_rows, sink, status);
+    }
     return TW_LAUNCH_CHECK();
 }

@@ -1081,6 +1081,108 @@ TW_EXPORT int tw_kv_store(const void* rows, int stride, int k_col, int v_col, co
 }
 
 // ---------------------------------------------------------------------------
+// What a token's projected row needs before an attention kernel can read the cache, in one pass (a block per token):
+//   1. RMS norm of up to two spans of heads, as tw_span_rmsnorm does; span 0 may be written to rows of its own
+//      (`dst0`, contiguous rows of heads0 * dim0 values) instead of in place;
+//   2. rotation by position of `rot_dims` values from column `rot_col` on (one span that all heads share, outside
+//      the normalised spans; pairs of neighbours or of halves), cos and sin multiplied by `magnitude`;
+//   3. the store of the key columns (from `k_col`) and, where the values have pages of their own, of the value
+//      columns (from `v_col`) into the token's place in its request's pages.
+// Serves attention with normalised heads (spans: the query heads, the key heads; no rotation) and attention over
+// low-rank latents (spans: the query latent, the key/value latent; the shared rotated key part; one set of pages).
+// Everything between the loads and the stores is fp32; what is stored is what the rows hold afterwards, bit for bit.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_rotate_store_kernel(T* __restrict__ rows, int row_stride, NormSpans sp, T* __restrict__ dst0, float eps,
+                         int rot_col, int rot_dims, const float* __restrict__ inv_freq, int interleaved, float magnitude,
+                         int k_col, int v_col, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                         const int* __restrict__ seq_slot, const int* __restrict__ block_table, int table_stride,
+                         T* __restrict__ k_cache, T* __restrict__ v_cache, int Hkv, int Dk, int Dv, int page_size, int num_pages,
+                         int write_cache, int* status) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int n = blockIdx.x;
+    const int s = seq_of_token[n];
+    if (s < 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    T* row = rows + (size_t)n * row_stride;
+    const int total = sp.heads[0] + sp.heads[1];
+    for (int item = warp; item < total; item += warps) {
+        const int span = item < sp.heads[0] ? 0 : 1;
+        const int head = span ? item - sp.heads[0] : item;
+        const int D = sp.dim[span];
+        T* x = row + sp.col[span] + (size_t)head * D;
+        T* y = (span == 0 && dst0) ? dst0 + (size_t)n * sp.heads[0] * D + (size_t)head * D : x;
+        const float* w = sp.weight[span];
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) {
+            const float v = tw_to_float(x[i]);
+            ss += v * v;
+        }
+        ss = tw_warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+        for (int i = lane; i < D; i += 32) y[i] = tw_from_float<T>((tw_to_float(x[i]) * inv) * w[i]);
+    }
+    const int pos = positions[n];
+    const int half = rot_dims >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const int a = rot_col + (interleaved ? 2 * i : i), b = rot_col + (interleaved ? 2 * i + 1 : i + half);
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
+        const float u = tw_to_float(row[a]), v = tw_to_float(row[b]);
+        row[a] = tw_from_float<T>(u * cs - v * sn);
+        row[b] = tw_from_float<T>(v * cs + u * sn);
+    }
+    if (!write_cache) return;
+    __syncthreads();            // the block's own writes to the row are visible to all of its threads from here on
+    const int blk = pos / page_size, in_page = pos - blk * page_size;
+    const int page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
+        return;
+    }
+    for (int i = threadIdx.x; i < Hkv * Dk; i += blockDim.x) {
+        const int h = i / Dk, d = i - h * Dk;
+        k_cache[(((size_t)page * Hkv + h) * page_size + in_page) * Dk + d] = row[k_col + i];
+    }
+    if (!v_cache) return;        // the values are the keys: one set of pages
+    for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
+        const int h = i / Dv, d = i - h * Dv;
+        v_cache[(((size_t)page * Hkv + h) * page_size + in_page) * Dv + d] = row[v_col + i];
+    }
+}
+
+TW_EXPORT int tw_norm_rotate_store(void* rows, int row_stride, int n_tokens, int spans, int col0, int heads0, int dim0,
+                                   const float* weight0, void* dst0, int col1, int heads1, int dim1, const float* weight1, float eps,
+                                   int rot_col, int rot_dims, const float* inv_freq, int interleaved, float magnitude, int k_col,
+                                   int v_col, const int* positions, const int* seq_of_token, const int* seq_slot,
+                                   const int* block_table, int table_stride, void* k_cache, void* v_cache, int Hkv, int Dk, int Dv,
+                                   int page_size, int num_pages, int write_cache, int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (spans < 0 || spans > 2 || (spans >= 1 && (heads0 <= 0 || dim0 <= 0 || !weight0)) || (spans == 2 && (heads1 <= 0 || dim1 <= 0 || !weight1))
+        || rot_dims < 0 || (rot_dims & 1) || (rot_dims && !inv_freq) || (write_cache && !k_cache))
+        return (int)cudaErrorInvalidValue;
+    NormSpans sp;
+    sp.count = spans;
+    sp.col[0] = col0; sp.heads[0] = spans >= 1 ? heads0 : 0; sp.dim[0] = dim0; sp.weight[0] = weight0;
+    sp.col[1] = col1; sp.heads[1] = spans == 2 ? heads1 : 0; sp.dim[1] = dim1; sp.weight[1] = weight1;
+    const int total = sp.heads[0] + sp.heads[1];
+    const int threads = total >= 8 ? 256 : 128;
+    if (dtype == TW_F32)
+        return tw_launch(norm_rotate_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, 1, (float*)rows, row_stride, sp,
+                         (float*)dst0, eps, rot_col, rot_dims, inv_freq, interleaved, magnitude, k_col, v_col, positions, seq_of_token,
+                         seq_slot, block_table, table_stride, (float*)k_cache, (float*)v_cache, Hkv, Dk, Dv, page_size, num_pages,
+                         write_cache, status);
+    return tw_launch(norm_rotate_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 1, (__nv_bfloat16*)rows,
+                     row_stride, sp, (__nv_bfloat16*)dst0, eps, rot_col, rot_dims, inv_freq, interleaved, magnitude, k_col, v_col,
+                     positions, seq_of_token, seq_slot, block_table, table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                     Hkv, Dk, Dv, page_size, num_pages, write_cache, status);
+}
+
+// ---------------------------------------------------------------------------
 // acc = (first ? 0 : acc) + scale * x, element by element in fp32; `out` (may be null) receives the new acc in
 // the activation type.  For mixers whose result is a weighted sum of several mixers' results.
 // ---------------------------------------------------------------------------

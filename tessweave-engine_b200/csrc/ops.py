@@ -496,6 +496,46 @@ def span_rmsnorm(rows: torch.Tensor, n_rows: int, spans: list[tuple[int, int, in
     _check(code, "span_rmsnorm")
 
 
+def norm_rotate_store(rows: torch.Tensor, n_tokens: int, spans: list[tuple[int, int, int, torch.Tensor]], eps: float,
+                      positions: torch.Tensor, seq_of_token: torch.Tensor, seq_slot: torch.Tensor, block_table: torch.Tensor,
+                      k_pages: torch.Tensor, v_pages: torch.Tensor | None, k_col: int, v_col: int, write_cache: bool,
+                      status: torch.Tensor, dst0: torch.Tensor | None = None, rot_col: int = 0, rot_dims: int = 0,
+                      inv_freq: torch.Tensor | None = None, interleaved: bool = False, magnitude: float = 1.0) -> None:
+    """One pass over every token's projected row: the norms of ``spans`` (as ``span_rmsnorm``; span 0 goes to the
+    contiguous rows ``dst0`` instead of in place where given), the rotation by position of ``rot_dims`` values from
+    column ``rot_col`` on (``rotate_pairs`` on one span), and the store of the key columns (from ``k_col``) and value
+    columns (from ``v_col``; ``v_pages`` None: one set of pages) into the token's place in the pages."""
+    _need(len(spans) <= 2, "norm_rotate_store: at most two spans")
+    _cuda(rows, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status, dst0, inv_freq, *(w for _, _, _, w in spans))
+    _need(rows.dim() == 2 and rows.stride(1) == 1 and rows.shape[0] >= n_tokens and rows.dtype == k_pages.dtype and k_pages.is_contiguous(),
+          "norm_rotate_store: rows of the pages' type, contiguous pages")
+    for col, heads, dim, w in spans:
+        _need(col >= 0 and heads > 0 and dim > 0 and col + heads * dim <= rows.shape[1] and w.dtype == torch.float32
+              and w.numel() == dim and w.is_contiguous(), "norm_rotate_store: a span must lie inside the rows, with an fp32 weight per value of a head")
+    _need(dst0 is None or (spans and dst0.is_contiguous() and dst0.dtype == rows.dtype and dst0.shape[0] >= n_tokens
+                           and dst0.shape[1] == spans[0][1] * spans[0][2]), "norm_rotate_store: the rows of span 0 must be contiguous and of its width")
+    _need(rot_dims % 2 == 0 and rot_dims >= 0 and rot_col >= 0 and rot_col + rot_dims <= rows.shape[1]
+          and (rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2)),
+          "norm_rotate_store: the rotated span must lie inside the rows, with an fp32 rate per pair")
+    _need(v_pages is None or (v_pages.dtype == rows.dtype and v_pages.is_contiguous() and k_pages.shape[:3] == v_pages.shape[:3]),
+          "norm_rotate_store: value pages must be contiguous, of the rows' type and as many as the key pages")
+    kv_heads, dk = k_pages.shape[1], k_pages.shape[3]
+    dv = 0 if v_pages is None else v_pages.shape[3]
+    _need(k_col + kv_heads * dk <= rows.shape[1] and (v_pages is None or v_col + kv_heads * dv <= rows.shape[1]),
+          "norm_rotate_store: the key and value columns must lie inside the rows")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "norm_rotate_store: bad block table")
+    (c0, h0, d0, w0) = spans[0] if spans else (0, 0, 0, None)
+    (c1, h1, d1, w1) = spans[1] if len(spans) == 2 else (0, 0, 0, None)
+    code = _fn("elementwise", "tw_norm_rotate_store")(
+        _ptr(rows), c_int(rows.stride(0)), c_int(n_tokens), c_int(len(spans)), c_int(c0), c_int(h0), c_int(d0), _ptr(w0), _ptr(dst0),
+        c_int(c1), c_int(h1), c_int(d1), _ptr(w1), c_float(eps), c_int(rot_col), c_int(rot_dims), _ptr(inv_freq),
+        c_int(1 if interleaved else 0), c_float(magnitude), c_int(k_col), c_int(v_col), _ptr(positions), _ptr(seq_of_token),
+        _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(kv_heads), c_int(dk),
+        c_int(dv), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), c_int(1 if write_cache else 0), c_int(dtype_code(rows.dtype)),
+        _ptr(status), _stream())
+    _check(code, "norm_rotate_store")
+
+
 def gate_mul(out: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, act: int, n_rows: int) -> None:
     """out = x * act(gate) element by element (``GATE_SIGMOID`` or ``GATE_SILU``), fp32 arithmetic; the three may be
     column slices of wider rows and ``out`` may be ``x``."""
@@ -560,7 +600,7 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, positions: torch.Tenso
     _need(bias_by_distance is None or (bias_by_distance.dtype == torch.float32 and bias_by_distance.dim() == 2
                                        and bias_by_distance.shape[1] == n_q_heads and bias_by_distance.is_contiguous()
                                        and bias_by_distance.shape[0] > 0), "attention: the distance bias must be fp32 [rows, Hq]")
-    _need(head_dim <= 256 and v_pages.shape[3] <= 256, f"attention: head sizes above 256 are not supported")
+    _need(head_dim <= 1024 and v_pages.shape[3] <= 1024, "attention: head sizes above 1024 are not supported")
     _need(k_pages.shape[3] == head_dim and k_pages.shape[:3] == v_pages.shape[:3] and k_pages.is_contiguous()
           and v_pages.is_contiguous(), "attention: pages must be contiguous [pages, kv_heads, page, head size]")
     _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")

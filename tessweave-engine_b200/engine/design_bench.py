@@ -491,3 +491,185 @@ def nufatar_kernel_table(config: dict, batch: int, context: int, prefill_tokens:
     if int(status) != 0:
         raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
     return rows
+
+
+# ---------------------------------------------------------------------------
+# the Dugudra decoder
+# ---------------------------------------------------------------------------
+def dugudra_config_like(qwen: dict, layers: int) -> dict:
+    """A Dugudra config.json with the sizes of the Qwen2 configuration ``qwen``: layers [attention, latent attention,
+    gla, latent attention] in turn, each with eight experts of a quarter of the dense feed-forward's size and two
+    identity experts (three chosen).  The attention has Qwen2's head counts and head size and a window of 1,024; the
+    latent attention has as many heads of the same size with half as many rotated values more, a query latent of 1,536
+    and cached rows of 192 + 64 values, the same window; gla has half as many heads of the same size."""
+    heads, kv, dim, width = qwen["num_attention_heads"], qwen["num_key_value_heads"], qwen["head_dim"], qwen["hidden_size"]
+    mlp = {"kind": "moe", "expert": {"ff": qwen["intermediate_size"] // 4, "limit": 7.0},
+           "router": {"experts": 8, "identity": 2, "top": 3, "scale": 1.5}}
+    half = max(1, heads // 2)
+    attention = {"type": "attention", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                                                            "scale": dim ** -0.5, "mask": {"size": 1024}}}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "q_rank": 1536, "kv_rank": 256 - dim // 2,
+        "scale": (dim + dim // 2) ** -0.5, "mask": {"size": 1024},
+        "rot": {"dims": dim // 2, "base": qwen["rope_theta"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    gla = {"type": "gla", "mlp": mlp, "mixer": {"heads": half, "dim": dim, "vdim": dim, "tau": 16.0, "decay_rank": 64}}
+    pattern = [attention, latent, gla, latent]
+    return {"architecture": "Dugudra", "vocab": qwen["vocab_size"], "width": width, "norm": {"eps": qwen["rms_norm_eps"]},
+            "embedding": {"scale": width ** 0.5}, "residual_mult": 0.7, "logit_softcap": 30.0,
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def dugudra_kernel_table(config: dict, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, tflops: float,
+                         page_size: int = 16) -> list[dict]:
+    """The Dugudra kernels alone, each inside a CUDA graph with operands rotated beyond L2, for a decode step of
+    ``batch`` rows and a prompt step: both attentions over their caches (norms, rotation, store, the per-head maps of the
+    latent kind, attention), the gla recurrence, the norm over heads with its gate, the routed experts with identity
+    experts, and the norm that adds a scaled delta.  fraction = max(bytes / HBM peak, FLOPs / tensor peak) / time."""
+    import tessweave_engine_b200 as tw
+    from ..models.dugudra import experts_spec, mixer_spec
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    rt = Runtime(dev, bf)
+    cfg, _ = tw.resolve(config)
+    W = cfg.width
+    layer_of = {l.type: l for l in cfg.layers}
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows: list[dict] = []
+
+    def add(name, m, thunks, nbytes, flops, reps=4, note=""):
+        kernel = _kernels_of(thunks[0])
+        us = _graph_us(thunks, reps)
+        floor = max(nbytes / (hbm_gbs * 1e9), flops / (tflops * 1e12)) * 1e6
+        rows.append({"op": name, "rows": m, "kernel": kernel, "us": round(us, 2), "mbytes": round(nbytes / 1e6, 2),
+                     "gflop": round(flops / 1e9, 2), "floor_us": round(floor, 2), "frac": round(floor / us, 3),
+                     "bound": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (tflops * 1e12) else "tensor", "note": note})
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)     # noqa: E731
+    for m, phase in ((batch, "decode"), (prefill_tokens, "prefill")):
+        requests = batch if phase == "decode" else 1
+        per = m // requests
+        slots, starts, lens = i32(list(range(requests))), i32([r * per for r in range(requests)]), i32([per] * requests)
+        seq_of = i32([r for r in range(requests) for _ in range(per)])
+        positions = i32([context - 1] * m if phase == "decode" else list(range(m)))
+        ws = Workspace(dev)
+        ctx = _context(rt, ws, status, positions.tolist(), seq_of.tolist(), list(range(requests)), starts.tolist(), lens.tolist(),
+                       [context] * requests if phase == "decode" else [m])
+        kv_tokens = context if phase == "decode" else m
+        blocks = -(-kv_tokens // page_size)
+
+        def caches_for(att, per_key):
+            out = []
+            for _ in range(_copies(requests * blocks * page_size * per_key)):
+                cache = CacheManager([(att.cache_need(), None)], page_size, requests * blocks, requests, kv_tokens, bf, dev,
+                                     prefix_cache=False)
+                for g in cache.groups:
+                    g.k.normal_(0, 0.5)
+                    if g.v is not g.k:
+                        g.v.normal_(0, 0.5)
+                for _r in range(requests):
+                    cache.ensure(cache.admit(None), kv_tokens)
+                cache.sync_tables()
+                out.append(cache)
+            return out
+
+        # ---- attention with normalised heads and a sink: norms + store, attention
+        side = layer_of["attention"].mixer
+        att = build_part("mixer", mixer_spec(cfg, layer_of["attention"], "bench"), rt)
+        _fill(att)
+        Hq, G, D = att.n_heads, att.n_kv_heads, att.head_dim
+        seen = min(kv_tokens, side.window) if side.window else kv_tokens
+        per_key = G * D * 2 * 2
+        caches = caches_for(att, per_key)
+        views = [c.view(0) for c in caches]
+        projs = [torch.randn(m, att.qkv_width, device=dev, dtype=bf) for _ in range(_copies(m * att.qkv_width * 2) if phase == "prefill" else 1)]
+        if phase == "decode":
+            nbytes, flops = m * seen * per_key + m * (att.qkv_width + att.out_size) * 2, 2.0 * m * Hq * 2 * D * seen
+        else:
+            nbytes = m * (att.qkv_width * 2 + att.out_size) * 2 + m * per_key
+            flops = 2.0 * Hq * 2 * D * (seen * (m - seen) + seen * (seen + 1) / 2)
+        add(f"{phase}: attention over a window of {side.window}, normalised heads, sink", m,
+            [(lambda v=v, i=i: att.attend(ctx, projs[i % len(projs)], v, True)) for i, v in enumerate(views)], nbytes, flops,
+            reps=2 if phase == "prefill" else 4)
+        del caches, views, projs, att
+        torch.cuda.empty_cache()
+        # ---- latent attention: norms + rotation + store + queries into the latent space; attention; value maps + gate
+        side = layer_of["latent_attention"].mixer
+        lat = build_part("mixer", mixer_spec(cfg, layer_of["latent_attention"], "bench"), rt)
+        _fill(lat)
+        Hq, Dl, C = lat.n_heads, lat.head_dim, lat.kv_rank
+        seen = min(kv_tokens, side.window) if side.window else kv_tokens
+        per_key = Dl * 2
+        caches = caches_for(lat, per_key)
+        views = [c.view(0) for c in caches]
+        projs = [torch.randn(m, lat.in_width, device=dev, dtype=bf) for _ in range(_copies(m * lat.in_width * 2) if phase == "prefill" else 1)]
+        maps = Hq * (lat.q_head * lat.q_rank + lat.q_head * Dl) * 2
+        add(f"{phase}: latent norms + rotation + store, query product, rotation, queries into the latent space", m,
+            [(lambda v=v, i=i: lat.prepare(ctx, projs[i % len(projs)], v, True)) for i, v in enumerate(views)],
+            m * (lat.in_width + lat.q_rank + Dl + Hq * (2 * lat.q_head + Dl)) * 2 + maps,
+            2.0 * m * Hq * lat.q_head * (lat.q_rank + Dl), note="the two products are the library's")
+        ql = lat.prepare(ctx, projs[0], views[0], True).clone()
+        outs = [torch.empty(m, lat.q_size, device=dev, dtype=bf) for _ in range(2)]
+        if phase == "decode":
+            nbytes, flops = m * seen * per_key + m * 2 * lat.q_size * 2, 2.0 * m * Hq * 2 * Dl * seen
+        else:
+            nbytes = m * (2 * lat.q_size + Dl) * 2
+            flops = 2.0 * Hq * 2 * Dl * (seen * (m - seen) + seen * (seen + 1) / 2)
+        add(f"{phase}: attention of {Hq} heads over cached rows of {Dl} values (keys and values at once), window {side.window}", m,
+            [(lambda v=v, i=i: lat._attend(ctx, outs[i % 2], ql, v)) for i, v in enumerate(views)], nbytes, flops,
+            reps=2 if phase == "prefill" else 4)
+        del caches, views, projs, lat, ql, outs
+        torch.cuda.empty_cache()
+        # ---- gla: the recurrence, then the norm over heads with its gate
+        side = layer_of["gla"].mixer
+        H, Dk, Dv = side.heads, side.dim, side.vdim
+        numel = ops.recurrence_state_numel(ops.RECURRENCE_GLA, H, Dk, Dv)
+        sets = []
+        for _ in range(_copies(max(requests * numel * 8, m * H * (2 * Dk + Dv) * 2))):
+            q, k, v = (torch.randn(m, H * d, device=dev, dtype=bf) * 0.3 for d in (Dk, Dk, Dv))
+            sets.append((q, k, v, torch.zeros(requests, numel, device=dev), torch.empty(m, H * Dv, device=dev),
+                         torch.randn(m, H * Dk, device=dev)))
+        bias = torch.full((H * Dk,), 3.0, device=dev)
+        add(f"{phase}: gla recurrence, {H} heads of {Dk} x {Dv}", m,
+            [(lambda s=s: ops.linear_recurrence(ops.RECURRENCE_GLA, s[4], None, s[0], s[1], s[2], s[3], positions, slots, starts, lens,
+                                                requests, H, Dk, Dv, True, max_q_len=per, pre=s[5], p0=bias, q_scale=Dk ** -0.5,
+                                                cap=1.0 / side.tau)) for s in sets],
+            m * H * (2 * Dk + Dv) * 2 + m * H * Dv * 4 + 2 * requests * numel * 4 + m * H * Dk * 4, 0.0,
+            reps=2 if phase == "prefill" else 8, note=f"{4.0 * m * H * Dk * Dv / 1e9:.2f} GFLOP of fp32 multiply-adds outside the tensor cores")
+        del sets
+        sets = [(torch.randn(m, H * Dv, device=dev), torch.randn(m, H * Dv, device=dev, dtype=bf), torch.empty(m, H * Dv, device=dev, dtype=bf))
+                for _ in range(_copies(m * H * Dv * 8))]
+        nw = torch.ones(H * Dv, device=dev)
+        add(f"{phase}: norm over each head + gate", m,
+            [(lambda r=r, g=g, o=o: ops.head_norm_gate(o, r, None, nw, g, ops.GATE_SILU, 1e-6, m, H, Dv)) for r, g, o in sets],
+            m * H * Dv * 8, 0.0, reps=8)
+        del sets
+        # ---- routed experts with identity experts and the clamped activation
+        mlp = layer_of["attention"].mlp
+        parts = []
+        for _ in range(_copies(mlp.experts * 3 * mlp.ff * W * 2) if phase == "decode" else 2):
+            part = build_part("feed_forward", experts_spec(cfg, mlp), rt)
+            _fill(part)
+            part.w_router.normal_(0, 0.5)
+            part.correction.normal_(0, 0.05)
+            parts.append(part)
+        hs = [torch.randn(m, W, device=dev, dtype=bf) for _ in range(4)]
+        touched = min(mlp.experts, m * mlp.top)
+        add(f"{phase}: router over {mlp.experts} + {mlp.identity} outputs, {mlp.top} chosen", m,
+            [(lambda p=p, i=i: p.route(ctx, hs[i % 4])) for i, p in enumerate(parts)], m * W * 2 + (mlp.experts + mlp.identity) * W * 2, 0.0, reps=8)
+        add(f"{phase}: the chosen experts' gate/up, clamped activation, down and the weighted sum", m,
+            [(lambda p=p, i=i: p.forward(ctx, hs[i % 4])) for i, p in enumerate(parts)],
+            touched * 3 * mlp.ff * W * 2 + m * W * 4, 2.0 * m * mlp.top * 3 * mlp.ff * W * mlp.experts / (mlp.experts + mlp.identity), reps=2,
+            note="includes the router; bytes: the matrices of the experts a step of this size touches at most, once")
+        del parts
+        # ---- the norm that adds a scaled delta
+        norm = build_part("norm", tw.PartSpec("rmsnorm", {"size": W, "eps": cfg.norm_eps, "weight_name": ""}), rt)
+        _fill(norm)
+        sets = [(torch.randn(m, W, device=dev), torch.randn(m, W, device=dev, dtype=bf), torch.empty(m, W, device=dev, dtype=bf))
+                for _ in range(_copies(m * W * 12))]
+        add(f"{phase}: residual add of a scaled delta + RMSNorm", m,
+            [(lambda r=r, d=d, o=o: norm.apply(ctx, o, r, d, m, delta_scale=cfg.residual_mult)) for r, d, o in sets],
+            m * W * (4 + 2 + 4 + 2), 0.0, reps=8)
+        del sets
+        torch.cuda.empty_cache()
+    if int(status) != 0:
+        raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
+    return rows

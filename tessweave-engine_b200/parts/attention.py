@@ -28,7 +28,8 @@ class PagedSoftmaxMixer(Mixer):
         group = self.n_heads // self.n_kv_heads
         tma = not self.score_terms and ops.decode_tma_supported(self.runtime.dtype, self.head_dim, cache.page_size)
         splits = ops.decode_tma_splits if tma else ops.decode_splits
-        nsplit = splits(ctx.n_seqs, self.n_kv_heads, group, ctx.max_kv_len)
+        # (the keys a request can see: a window bounds them, and the kernels cut those into the slices)
+        nsplit = splits(ctx.n_seqs, self.n_kv_heads, group, min(ctx.max_kv_len, self.window) if self.window else ctx.max_kv_len)
         return tma, nsplit, ctx.n_seqs * self.n_kv_heads * -(-group // 8) * nsplit
 
     def _attend_tensor_cores(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, cache: PagedView) -> None:
@@ -109,7 +110,8 @@ class GQAAttention(PagedSoftmaxMixer):
     flow_engine/cache.py:93-100 (slots).  Weight names are the checkpoint's (``names`` replaces them).
 
     ``v_head_dim``: the size of a value head where it differs from ``head_dim`` (the size of a query and a key
-    head); the output then has ``n_heads`` heads of that size.  Such a mixer, and one whose position encoding no
+    head); the output then has ``n_heads`` heads of that size.  Heads above 256 (up to 1024) attend with the exact
+    kernel in both run types.  Such a mixer, and one whose position encoding no
     kernel applies on the way, adds the bias, applies the encoding and stores keys and values as separate
     steps, and attends with the exact kernel; everything else takes the fused and tensor-core kernels.
 
@@ -141,16 +143,16 @@ class GQAAttention(PagedSoftmaxMixer):
         super().__init__(runtime)
         if min(hidden, n_heads, n_kv_heads, head_dim) <= 0 or n_heads % n_kv_heads:
             raise ValueError("attention: heads must be positive and n_heads a multiple of n_kv_heads")
-        if (head_dim % 2 and position.kind != "none") or head_dim > 256:
-            raise ValueError(f"attention: head_dim {head_dim} must be at most 256, and even where heads are rotated")
+        if (head_dim % 2 and position.kind != "none") or head_dim > 1024:
+            raise ValueError(f"attention: head_dim {head_dim} must be at most 1024, and even where heads are rotated")
         if out_bias:
             raise ValueError("attention: a bias on the output projection is not implemented")
         if window is not None and window <= 0:
             raise ValueError("attention: window must be positive or None")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
         self.v_dim = head_dim if v_head_dim is None else int(v_head_dim)
-        if not 0 < self.v_dim <= 256:
-            raise ValueError(f"attention: v_head_dim {self.v_dim} must lie in 1..256")
+        if not 0 < self.v_dim <= 1024:
+            raise ValueError(f"attention: v_head_dim {self.v_dim} must lie in 1..1024")
         self.same_dims = self.v_dim == head_dim
         self.values_are_keys = bool(values_are_keys)
         if self.values_are_keys and (not self.same_dims or qkv_bias):
@@ -304,8 +306,15 @@ class GQAAttention(PagedSoftmaxMixer):
             if self.b_qkv is not None:
                 ops.add_bias_rows(qkv, self.b_qkv, n)
             if self.qk_norm is not None:
-                ops.span_rmsnorm(qkv, n, [(0, self.n_heads, self.head_dim, self.q_norm_w),
-                                          (self.q_size, self.n_kv_heads, self.head_dim, self.k_norm_w)], self.qk_norm["eps"])
+                spans = [(0, self.n_heads, self.head_dim, self.q_norm_w), (self.q_size, self.n_kv_heads, self.head_dim, self.k_norm_w)]
+                if self.position.kind == "none":
+                    # the norms of the heads and the store in one pass over the token's row
+                    ops.norm_rotate_store(qkv, n, spans, self.qk_norm["eps"], ctx.positions, ctx.seq_of_token, ctx.seq_slot,
+                                          cache.block_table, cache.k_pages, None if self.values_are_keys else cache.v_pages,
+                                          self.q_size, self.q_size + self.kv_size, write_cache, ctx.status)
+                    self._attend(ctx, out, qkv, cache)
+                    return out
+                ops.span_rmsnorm(qkv, n, spans, self.qk_norm["eps"])
             self.position.apply(ctx, qkv, self.n_heads + self.n_kv_heads, self.head_dim)
             if write_cache:
                 ops.kv_store(qkv, self.q_size, self.q_size + self.kv_size, ctx.positions, ctx.seq_of_token, ctx.seq_slot,

@@ -25,7 +25,8 @@ class LatentAttention(PagedSoftmaxMixer):
     kv_rank + rot_dim whose keys are the rows [c | r] of ONE key/value head and whose values are the same rows (the
     last rot_dim values of a result are not used); the head's value map is applied to the attention's result,
     o_h = Wuv_h (sum_j p_j c(j)).  The cache keeps [c | r] per token and nothing else (``values_are_keys``), and the
-    paged kernels of the other attention mixers serve this one: exact, mma.sync prefill and split-KV decode.
+    paged kernels of the other attention mixers serve this one: exact, mma.sync prefill and split-KV decode (cached
+    rows of more than 256 values: the exact kernel in both run types).
 
     The two per-head maps are batched library products.  The first one also moves b_h into place: head h multiplies by
     [[Wuk_h, 0], [0, I]], built once when the weights are in (the identity block copies bit for bit).
@@ -43,8 +44,8 @@ class LatentAttention(PagedSoftmaxMixer):
         super().__init__(runtime)
         if min(hidden, n_heads, head_dim, v_head_dim, q_rank, kv_rank) <= 0 or rot_dim < 0 or rot_dim % 2:
             raise ValueError("latent_attention: sizes must be positive and the rotated part even")
-        if kv_rank + rot_dim > 256:
-            raise ValueError(f"latent_attention: kv_rank + rot_dim = {kv_rank + rot_dim} is more than the attention kernels' 256")
+        if kv_rank + rot_dim > 1024:
+            raise ValueError(f"latent_attention: kv_rank + rot_dim = {kv_rank + rot_dim} is more than the attention kernels' 1024")
         if window is not None and window <= 0:
             raise ValueError("latent_attention: window must be positive or None")
         if not eps > 0:
@@ -102,12 +103,18 @@ class LatentAttention(PagedSoftmaxMixer):
         """h @ [Wdq; Wdkv; Wg].T: rows [query latent | c' | r | gate] before norms and rotation."""
         return linear(ctx, "latent.in", h, self.w_in)
 
-    def _rotate(self, ctx: StepContext, rows: torch.Tensor, n_heads: int, head_dim: int, first: int) -> None:
+    def _plan(self):
         if not self.rot_dim:
-            return
+            return None
         plan = self.position.rotary_plan(self.rot_dim)
         if plan is None or plan.rot_dims != self.rot_dim:
             raise ValueError("latent_attention: the position encoding must be a rotation of pairs over the whole rotated part")
+        return plan
+
+    def _rotate(self, ctx: StepContext, rows: torch.Tensor, n_heads: int, head_dim: int, first: int) -> None:
+        plan = self._plan()
+        if plan is None:
+            return
         ops.rotate_pairs(rows, ctx.positions, ctx.seq_of_token, plan.inv_freq, ctx.n_tokens, n_heads, head_dim, plan.rot_dims,
                          plan.interleaved, magnitude=plan.magnitude, first=first)
 
@@ -115,12 +122,17 @@ class LatentAttention(PagedSoftmaxMixer):
         """Norms, rotation, the store of [c | r], and the queries in the latent space: [rows, H * (kv_rank + rot_dim)]."""
         n, ws, dt, H = ctx.n_tokens, ctx.workspace, self.runtime.dtype, self.n_heads
         a = self.q_rank
-        ops.span_rmsnorm(proj, n, [(0, 1, self.q_rank, self.q_norm_w), (a, 1, self.kv_rank, self.c_norm_w)], self.eps)
-        self._rotate(ctx, proj[:, a:a + self.head_dim], 1, self.head_dim, self.kv_rank)
-        if write_cache:
-            ops.kv_store(proj, a, a, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table, cache.k_pages, None, n,
-                         ctx.status)
-        q = linear(ctx, "latent.q", proj[:, :a], self.w_uq)
+        # one pass over a token's row: both latents' norms (the query latent into rows of its own, which the next
+        # product reads), the rotation of the shared key part, the store of [c | r]
+        plan = self._plan()
+        cq = ws.get("latent.cq", (n, a), dt)
+        ops.norm_rotate_store(proj, n, [(0, 1, self.q_rank, self.q_norm_w), (a, 1, self.kv_rank, self.c_norm_w)], self.eps,
+                              ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table, cache.k_pages, None, a, a,
+                              write_cache, ctx.status, dst0=cq, rot_col=a + self.kv_rank, rot_dims=self.rot_dim,
+                              inv_freq=plan.inv_freq if plan is not None else None,
+                              interleaved=plan.interleaved if plan is not None else False,
+                              magnitude=plan.magnitude if plan is not None else 1.0)
+        q = linear(ctx, "latent.q", cq, self.w_uq)
         self._rotate(ctx, q, H, self.q_head, self.plain_dim)
         ql = ws.get("latent.q_latent", (n, self.q_size), dt)
         configure_matmul_precision()

@@ -104,7 +104,7 @@ def edit(cfg, path, value):
     (("layers", 0, "type"), "mamba", "not implemented"),
     (("layers", 0, "mixer", "rot", "dims"), 4, "rot_dim"),
     (("layers", 0, "mixer", "rot_dim"), 7, "even"),
-    (("layers", 0, "mixer", "kv_rank"), 250, "not supported"),
+    (("layers", 0, "mixer", "kv_rank"), 1020, "not supported"),
     (("layers", 0, "mixer", "rot", "scaling", "factor"), 0.0, "positive"),
     (("layers", 0, "mixer", "mask", "size"), 0, "positive"),
     (("layers", 0, "mlp", "kind"), "dense", "not implemented"),
@@ -113,7 +113,7 @@ def edit(cfg, path, value):
     (("layers", 1, "mixer", "tau"), 0.0, "positive"),
     (("layers", 1, "mixer", "heads"), KeyError, "heads"),
     (("layers", 2, "mixer", "kv_heads"), 3, "multiple"),
-    (("layers", 2, "mixer", "dim"), 300, "not supported"),
+    (("layers", 2, "mixer", "dim"), 1300, "not supported"),
     (("norm", "eps"), 0.0, "positive"),
     (("logit_softcap",), -2.0, "positive"),
     (("width",), 0, "positive"),

@@ -142,7 +142,8 @@ def test_capped_logits(dtype):
 
 ATTENTION_SHAPES = [  # hidden, heads, kv heads, key size, value size, window, page
     (48, 4, 2, 16, 32, 9, 8), (40, 3, 1, 12, 20, 5, 4), (36, 5, 5, 7, 7, 3, 2), (64, 6, 3, 64, 64, 40, 16), (64, 2, 2, 32, 32, 150, 16),
-    (32, 1, 1, 8, 24, 2, 4), (128, 8, 2, 64, 64, 70, 16), (96, 4, 1, 80, 80, 33, 16), (64, 2, 1, 48, 16, None, 8)]
+    (32, 1, 1, 8, 24, 2, 4), (128, 8, 2, 64, 64, 70, 16), (96, 4, 1, 80, 80, 33, 16), (64, 2, 1, 48, 16, None, 8),
+    (64, 2, 1, 320, 272, 50, 16)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -172,7 +173,7 @@ LATENT_SHAPES = [  # hidden, heads, plain size, rotated size, value size, q late
     (48, 3, 16, 8, 24, 20, 40, 9, 8, 1000.0, yarn(4.0, 64, 8.0, 2.0)), (40, 5, 6, 2, 7, 5, 11, 3, 4, 10.0, None),
     (64, 4, 32, 16, 32, 64, 48, 24, 16, 2e4, yarn(16.0, 32, 16.0, 1.0)), (64, 4, 32, 16, 16, 48, 64, 150, 16, 2e4, yarn(8.0, 128, 32.0, 1.0)),
     (32, 1, 8, 4, 8, 8, 12, 2, 4, 50.0, yarn(1.0, 8, 2.0, 1.0)), (96, 12, 16, 16, 8, 32, 112, 40, 16, 3e5, yarn(4.0, 256, 32.0, 1.0)),
-    (64, 2, 8, 8, 8, 24, 24, None, 8, 5e4, None)]
+    (64, 2, 8, 8, 8, 24, 24, None, 8, 5e4, None), (64, 2, 16, 8, 16, 24, 300, 40, 16, 1e4, yarn(4.0, 64, 8.0, 2.0))]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -270,7 +271,7 @@ def test_one_key_at_the_window_edge(dtype, kind, page, window):
     wd = {k: v.double() for k, v in named(w).items()}
     length = 4 * window + 7
     t = length - 1
-    seen_sizes, unseen_sizes = [], []
+    seen_sizes, unseen_sizes, outputs = [], [], []
     for j in [t - window + 1, t - window, t - window + 2, t - 1, 0, 1, page - 1, page, (t - window + 1) // page * page]:
         h = 0.01 * torch.randn(length, hidden, generator=g)
         h[:, 0] = -1.0
@@ -281,11 +282,16 @@ def test_one_key_at_the_window_edge(dtype, kind, page, window):
         want = run_plain(h.double(), wd).float()
         for tail in (0, 1, 9):                           # the asking token inside a portion, alone, after single tokens
             got = edge_case(rt, mixer, page, h, tail)
-            close(got, want[-1:], dtype, f"key at {j} (edge at {t - window + 1}), last {tail} tokens alone", bf16=0.1)
+            outputs.append((f"key at {j} (edge at {t - window + 1}), last {tail} tokens alone", got, want[-1:]))
         (seen_sizes if 0 <= t - j < window else unseen_sizes).append(want[-1])
-    # the crafted key shows: the plain outputs with the key inside the window differ from those with it outside by their whole size
+    # the crafted key shows: the plain outputs with the key inside the window differ from those with it outside by their
+    # whole size (which is what every output is measured against: some of them are sums that cancel)
+    size = max(float(x.abs().max()) for x in seen_sizes + unseen_sizes)
     gap = float((seen_sizes[0] - unseen_sizes[0]).abs().max())
-    assert gap > 0.5 * float(seen_sizes[0].abs().max()) and gap > 0.2
+    assert gap > 0.4 * size and gap > 0.2
+    for what, got, want_row in outputs:
+        err = float((got - want_row).abs().max())
+        assert err <= (2e-5 if dtype == torch.float32 else 0.1) * size, f"{what}: differs by {err:.3g} (size {size:.3g})"
 
 
 GLA_SHAPES = [(48, 2, 16, 8, 4.0, 6), (40, 3, 10, 6, 1.0, 3), (64, 2, 32, 32, 16.0, 8), (36, 1, 16, 24, 2.0, 1), (96, 3, 32, 48, 16.0, 8),
