@@ -1092,9 +1092,10 @@ TW_EXPORT int tw_kv_store(const void* rows, int stride, int k_col, int v_col, co
 // low-rank latents (spans: the query latent, the key/value latent; the shared rotated key part; one set of pages).
 // Everything between the loads and the stores is fp32; what is stored is what the rows hold afterwards, bit for bit.
 // ---------------------------------------------------------------------------
+#define TW_NRS_MAXV 8       // values of a head a thread keeps in registers in the block-wide form
 template <typename T>
 __global__ void __launch_bounds__(256)
-norm_rotate_store_kernel(T* __restrict__ rows, int row_stride, NormSpans sp, T* __restrict__ dst0, float eps,
+norm_rotate_store_kernel(T* __restrict__ rows, int row_stride, NormSpans sp, T* __restrict__ dst0, float eps, int block_wide, int vec16,
                          int rot_col, int rot_dims, const float* __restrict__ inv_freq, int interleaved, float magnitude,
                          int k_col, int v_col, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                          const int* __restrict__ seq_slot, const int* __restrict__ block_table, int table_stride,
@@ -1108,23 +1109,102 @@ norm_rotate_store_kernel(T* __restrict__ rows, int row_stride, NormSpans sp, T* 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     T* row = rows + (size_t)n * row_stride;
     const int total = sp.heads[0] + sp.heads[1];
-    for (int item = warp; item < total; item += warps) {
-        const int span = item < sp.heads[0] ? 0 : 1;
-        const int head = span ? item - sp.heads[0] : item;
-        const int D = sp.dim[span];
-        T* x = row + sp.col[span] + (size_t)head * D;
-        T* y = (span == 0 && dst0) ? dst0 + (size_t)n * sp.heads[0] * D + (size_t)head * D : x;
-        const float* w = sp.weight[span];
-        float ss = 0.f;
-        for (int i = lane; i < D; i += 32) {
-            const float v = tw_to_float(x[i]);
-            ss += v * v;
-        }
-        ss = tw_warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-        for (int i = lane; i < D; i += 32) y[i] = tw_from_float<T>((tw_to_float(x[i]) * inv) * w[i]);
-    }
+    // the token's place in the pages is looked up first: a chain of dependent loads that the norms then hide
     const int pos = positions[n];
+    const int blk = pos / page_size, in_page = pos - blk * page_size;
+    const int page = (write_cache && blk < table_stride) ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
+    if (block_wide) {
+        // few heads of many values (a latent): the whole block takes a head at a time, its values kept in registers
+        __shared__ float scratch[33];
+        for (int item = 0; item < total; ++item) {
+            const int span = item < sp.heads[0] ? 0 : 1;
+            const int head = span ? item - sp.heads[0] : item;
+            const int D = sp.dim[span];
+            T* x = row + sp.col[span] + (size_t)head * D;
+            T* y = (span == 0 && dst0) ? dst0 + (size_t)n * sp.heads[0] * D + (size_t)head * D : x;
+            const float* w = sp.weight[span];
+            if constexpr (sizeof(T) == 2) {
+                if (vec16) {
+                    // rows, spans and weights on 16-byte boundaries: eight values per access, two accesses per thread
+                    const int nv = D >> 3;
+                    uint4 raw[2];
+                    float ss8 = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        raw[j] = make_uint4(0u, 0u, 0u, 0u);
+                        if (i < nv) {
+                            raw[j] = reinterpret_cast<const uint4*>(x)[i];
+                            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __bfloat1622float2(p2[e]);
+                                ss8 += f.x * f.x + f.y * f.y;
+                            }
+                        }
+                    }
+                    ss8 = tw_block_sum(ss8, scratch);
+                    const float inv8 = 1.0f / sqrtf(ss8 / (float)D + eps);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        if (i < nv) {
+                            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+                            const float4 wa = reinterpret_cast<const float4*>(w)[2 * i], wb = reinterpret_cast<const float4*>(w)[2 * i + 1];
+                            const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+                            uint4 packed;
+                            __nv_bfloat162* q2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __bfloat1622float2(p2[e]);
+                                q2[e] = __floats2bfloat162_rn((f.x * inv8) * ww[2 * e], (f.y * inv8) * ww[2 * e + 1]);
+                            }
+                            reinterpret_cast<uint4*>(y)[i] = packed;
+                        }
+                    }
+                    continue;
+                }
+            }
+            float v[TW_NRS_MAXV];
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < TW_NRS_MAXV; ++j) {
+                const int i = threadIdx.x + j * blockDim.x;
+                v[j] = i < D ? tw_to_float(x[i]) : 0.f;
+                ss += v[j] * v[j];
+            }
+            for (int i = threadIdx.x + TW_NRS_MAXV * blockDim.x; i < D; i += blockDim.x) {      // heads wider than the registers hold
+                const float u = tw_to_float(x[i]);
+                ss += u * u;
+            }
+            ss = tw_block_sum(ss, scratch);
+            const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int j = 0; j < TW_NRS_MAXV; ++j) {
+                const int i = threadIdx.x + j * blockDim.x;
+                if (i < D) y[i] = tw_from_float<T>((v[j] * inv) * w[i]);
+            }
+            for (int i = threadIdx.x + TW_NRS_MAXV * blockDim.x; i < D; i += blockDim.x)
+                y[i] = tw_from_float<T>((tw_to_float(x[i]) * inv) * w[i]);
+        }
+    } else {
+        for (int item = warp; item < total; item += warps) {
+            const int span = item < sp.heads[0] ? 0 : 1;
+            const int head = span ? item - sp.heads[0] : item;
+            const int D = sp.dim[span];
+            T* x = row + sp.col[span] + (size_t)head * D;
+            T* y = (span == 0 && dst0) ? dst0 + (size_t)n * sp.heads[0] * D + (size_t)head * D : x;
+            const float* w = sp.weight[span];
+            float ss = 0.f;
+            for (int i = lane; i < D; i += 32) {
+                const float v = tw_to_float(x[i]);
+                ss += v * v;
+            }
+            ss = tw_warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+            for (int i = lane; i < D; i += 32) y[i] = tw_from_float<T>((tw_to_float(x[i]) * inv) * w[i]);
+        }
+    }
     const int half = rot_dims >> 1;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const int a = rot_col + (interleaved ? 2 * i : i), b = rot_col + (interleaved ? 2 * i + 1 : i + half);
@@ -1138,11 +1218,27 @@ norm_rotate_store_kernel(T* __restrict__ rows, int row_stride, NormSpans sp, T* 
     }
     if (!write_cache) return;
     __syncthreads();            // the block's own writes to the row are visible to all of its threads from here on
-    const int blk = pos / page_size, in_page = pos - blk * page_size;
-    const int page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
     if (page < 0 || page >= num_pages) {
         if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
         return;
+    }
+    if constexpr (sizeof(T) == 2) {
+        if (vec16) {            // (the launcher has checked that key and value rows start and end on 16-byte boundaries)
+            const int kv8 = Dk >> 3;
+            for (int i = threadIdx.x; i < Hkv * kv8; i += blockDim.x) {
+                const int h = i / kv8, d = (i - h * kv8) << 3;
+                *reinterpret_cast<uint4*>(k_cache + (((size_t)page * Hkv + h) * page_size + in_page) * Dk + d) =
+                    *reinterpret_cast<const uint4*>(row + k_col + h * Dk + d);
+            }
+            if (!v_cache) return;
+            const int vv8 = Dv >> 3;
+            for (int i = threadIdx.x; i < Hkv * vv8; i += blockDim.x) {
+                const int h = i / vv8, d = (i - h * vv8) << 3;
+                *reinterpret_cast<uint4*>(v_cache + (((size_t)page * Hkv + h) * page_size + in_page) * Dv + d) =
+                    *reinterpret_cast<const uint4*>(row + v_col + h * Dv + d);
+            }
+            return;
+        }
     }
     for (int i = threadIdx.x; i < Hkv * Dk; i += blockDim.x) {
         const int h = i / Dk, d = i - h * Dk;
@@ -1170,14 +1266,24 @@ TW_EXPORT int tw_norm_rotate_store(void* rows, int row_stride, int n_tokens, int
     sp.col[0] = col0; sp.heads[0] = spans >= 1 ? heads0 : 0; sp.dim[0] = dim0; sp.weight[0] = weight0;
     sp.col[1] = col1; sp.heads[1] = spans == 2 ? heads1 : 0; sp.dim[1] = dim1; sp.weight[1] = weight1;
     const int total = sp.heads[0] + sp.heads[1];
-    const int threads = total >= 8 ? 256 : 128;
+    // a warp per head where there are many heads; the whole block per head where there are few heads of many values
+    const int widest = max(sp.heads[0] ? sp.dim[0] : 0, sp.heads[1] ? sp.dim[1] : 0);
+    const int block_wide = (total > 0 && total <= 2 && widest >= 128) ? 1 : 0;
+    const int threads = (block_wide ? widest >= 1024 : total >= 8) ? 256 : 128;
+    // 16-byte accesses (bfloat16 only): every span, the key and value columns, the rows and the pages start and end on
+    // 16-byte boundaries, and a head fits two accesses per thread
+    auto a16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    int vec16 = (dtype != TW_F32 && a16(rows) && a16(dst0) && a16(k_cache) && a16(v_cache) && a16(weight0) && a16(weight1)
+                 && (row_stride & 7) == 0 && (k_col & 7) == 0 && (Dk & 7) == 0 && (!v_cache || ((v_col & 7) == 0 && (Dv & 7) == 0))) ? 1 : 0;
+    for (int sidx = 0; sidx < 2; ++sidx)
+        if (sp.heads[sidx] && ((sp.col[sidx] & 7) || (sp.dim[sidx] & 7) || (block_wide && sp.dim[sidx] > 16 * threads))) vec16 = 0;
     if (dtype == TW_F32)
         return tw_launch(norm_rotate_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, 1, (float*)rows, row_stride, sp,
-                         (float*)dst0, eps, rot_col, rot_dims, inv_freq, interleaved, magnitude, k_col, v_col, positions, seq_of_token,
+                         (float*)dst0, eps, block_wide, 0, rot_col, rot_dims, inv_freq, interleaved, magnitude, k_col, v_col, positions, seq_of_token,
                          seq_slot, block_table, table_stride, (float*)k_cache, (float*)v_cache, Hkv, Dk, Dv, page_size, num_pages,
                          write_cache, status);
     return tw_launch(norm_rotate_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 1, (__nv_bfloat16*)rows,
-                     row_stride, sp, (__nv_bfloat16*)dst0, eps, rot_col, rot_dims, inv_freq, interleaved, magnitude, k_col, v_col,
+                     row_stride, sp, (__nv_bfloat16*)dst0, eps, block_wide, vec16, rot_col, rot_dims, inv_freq, interleaved, magnitude, k_col, v_col,
                      positions, seq_of_token, seq_slot, block_table, table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                      Hkv, Dk, Dv, page_size, num_pages, write_cache, status);
 }

@@ -295,7 +295,7 @@ def test_one_key_at_the_window_edge(dtype, kind, page, window):
 
 
 GLA_SHAPES = [(48, 2, 16, 8, 4.0, 6), (40, 3, 10, 6, 1.0, 3), (64, 2, 32, 32, 16.0, 8), (36, 1, 16, 24, 2.0, 1), (96, 3, 32, 48, 16.0, 8),
-              (64, 4, 64, 16, 8.0, 4)]
+              (64, 4, 64, 16, 8.0, 4), (64, 2, 48, 40, 3.0, 5), (40, 1, 24, 8, 16.0, 2), (128, 2, 128, 64, 16.0, 16), (96, 2, 96, 32, 6.0, 4)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
