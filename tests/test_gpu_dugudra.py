@@ -42,8 +42,8 @@ def mixer_of(rt, width, layer, eps=1e-5):
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("head_dim,first,dims,base,scaling", [
-    (24, 16, 8, 1e3, yarn(4.0, 64, 8.0, 2.0)), (16, 0, 16, 5e4, yarn(16.0, 32, 16.0, 1.0)), (40, 6, 32, 2e4, yarn(8.0, 1024, 32.0, 1.0)),
-    (12, 10, 2, 10.0, None), (64, 48, 16, 2e4, yarn(4.0, 512, 32.0, 1.0)), (20, 4, 4, 50.0, yarn(1.0, 8, 2.0, 1.0))])
+    (24, 16, 8, 1e3, yarn(4.0, 64, 8.0, 2.0)), (16, 0, 16, 5e4, yarn(16.0, 32, 16.0, 1.0)), (40, 6, 32, 7e4, yarn(8.0, 1024, 32.0, 1.0)),
+    (12, 10, 2, 10.0, None), (64, 48, 16, 3e4, yarn(4.0, 256, 32.0, 1.0)), (20, 4, 4, 50.0, yarn(1.0, 8, 2.0, 1.0))])
 def test_rotation_of_neighbours_inside_a_head(dtype, head_dim, first, dims, base, scaling):
     """Values first + 2i and first + 2i + 1 of a head turn together, at rates that the stretching slows for the pairs
     that turn rarely, and grow by 0.1 ln(factor) + 1; the rest of a head and what lies behind the heads stay."""
@@ -171,7 +171,7 @@ def test_attention_with_normed_heads_and_a_sink_alone(dtype, shape):
 
 LATENT_SHAPES = [  # hidden, heads, plain size, rotated size, value size, q latent, kv latent, window, page, base, scaling
     (48, 3, 16, 8, 24, 20, 40, 9, 8, 1000.0, yarn(4.0, 64, 8.0, 2.0)), (40, 5, 6, 2, 7, 5, 11, 3, 4, 10.0, None),
-    (64, 4, 32, 16, 32, 64, 48, 24, 16, 2e4, yarn(16.0, 32, 16.0, 1.0)), (64, 4, 32, 16, 16, 48, 64, 150, 16, 2e4, yarn(8.0, 128, 32.0, 1.0)),
+    (64, 4, 32, 16, 32, 64, 48, 24, 16, 3e4, yarn(16.0, 32, 16.0, 1.0)), (64, 4, 32, 16, 16, 48, 64, 150, 16, 5e3, yarn(8.0, 128, 32.0, 1.0)),
     (32, 1, 8, 4, 8, 8, 12, 2, 4, 50.0, yarn(1.0, 8, 2.0, 1.0)), (96, 12, 16, 16, 8, 32, 112, 40, 16, 3e5, yarn(4.0, 256, 32.0, 1.0)),
     (64, 2, 8, 8, 8, 24, 24, None, 8, 5e4, None), (64, 2, 16, 8, 16, 24, 300, 40, 16, 1e4, yarn(4.0, 64, 8.0, 2.0))]
 

@@ -63,7 +63,7 @@ DUGUDRA_C = {
     "architecture": "Dugudra", "vocab": 211, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 11.3},
     "residual_mult": 0.8, "logit_softcap": 30.0,
     "layers": [attention(8, 2, 64, 64, 0.11, 40, moe(8, 1, 2, 48, 1.0, 1.5)),
-               latent(4, 32, 16, 32, 64, 48, 0.14, 2e4, 24, yarn(16.0, 32, 16.0, 1.0), moe(4, 4, 4, 32, 3.0, 1.0)),
+               latent(4, 48, 16, 32, 64, 48, 0.14, 3e4, 24, yarn(16.0, 32, 16.0, 1.0), moe(4, 4, 4, 32, 3.0, 1.0)),
                gla(2, 32, 32, 16.0, 8),
                attention(4, 4, 32, 32, 0.2, None),
                latent(8, 16, 16, 16, 32, 16, 0.2, 100.0, None, yarn(2.0, 16, 4.0, 0.5), moe(8, 1, 2, 48, 1.0, 1.5))],
@@ -81,9 +81,9 @@ DUGUDRA_D = {
 # windows that prompts of hundreds of tokens pass many times, on pages of 16 that the windows give back on the way
 DUGUDRA_E = {
     "architecture": "Dugudra", "vocab": 300, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 9.8},
-    "residual_mult": 0.7, "logit_softcap": 15.0,
+    "residual_mult": 0.75, "logit_softcap": 12.0,
     "layers": [attention(4, 2, 64, 64, 0.125, 70, moe(6, 2, 2, 32, 1.0, 1.5)),
-               latent(4, 32, 16, 16, 48, 64, 0.14, 2e4, 150, yarn(8.0, 128, 32.0, 1.0), moe(6, 2, 2, 32, 1.0, 1.5)),
+               latent(4, 32, 16, 16, 48, 64, 0.14, 5e3, 150, yarn(8.0, 128, 32.0, 1.0), moe(6, 2, 2, 32, 1.0, 1.2)),
                gla(3, 32, 48, 16.0, 8)],
 }
 
