@@ -500,6 +500,39 @@ def test_batches_and_cuts_do_not_change_a_request(folders, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_slots_and_pages_used_again(dtype, folders, noise):
+    """One request slot and barely enough pages: each request gets the slot and the pages its predecessor gave back,
+    with the predecessor's states, latents and keys still in them (the manager zeroes the states at admission)."""
+    from tessweave_engine_b200.engine.runner import ModelRunner, StepEntry
+    name = "A"
+    model = tw.load_model(folders[name, dtype], dtype, "cuda")
+    cache = tw.CacheManager(model.cache_needs(), DUGUDRA_PAGE[name], 9, 1, 72, model.runtime.dtype, model.runtime.device,
+                            prefix_cache=False)
+    runner = ModelRunner(model, cache, 72, 1, cuda_graphs=False)
+    config, weights = plain.read_folder(folders[name, dtype], torch.float64)
+    _, moved = moved_weights(folders[name, dtype], 96)
+    for i, n in enumerate([70, 64, 3, 71]):
+        tokens = random_tokens(config["vocab"], n, 40 + i)
+        lease = cache.admit(None)
+        assert lease.slot == 0
+        cut = max(1, n // 2)
+        cache.ensure(lease, cut)
+        runner.step([StepEntry(lease.slot, tokens[:cut], 0, [])])
+        cache.ensure(lease, n)
+        got = runner.step([StepEntry(lease.slot, tokens[cut:], cut, list(range(n - cut)))]).cpu().numpy()
+        runner.check_status()
+        cache.release(lease)
+        cache.check_invariants()
+        want = plain.forward(config, weights, tokens).numpy()
+        if dtype == "float32":
+            low = plain.logits_of(folders[name, dtype], tokens, torch.float32).numpy()
+        else:
+            low = plain.forward(config, moved, tokens).float().numpy()
+        compare({("r", cut + k): got[k] for k in range(n - cut)}, {"r": want}, dtype, f"request {i} in a used slot",
+                {"r": [row_error(low[p], want[p]) for p in range(n)]})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_past_windows_and_pages(dtype, folders, tmp_path):
     """A short prompt and 300 tokens one by one: the windows pass over decoded tokens only, pages of the windowed
     layers are given back and used again on the way, the states carry everything else."""
