@@ -118,6 +118,11 @@ linear_recurrence_kernel(RecArgs a) {
                           && (!a.channel_decay || ((a.wpre_stride % 4) == 0 && (reinterpret_cast<size_t>(a.wpre) % 16) == 0
                                                    && (reinterpret_cast<size_t>(a.p1) % 16) == 0));
 
+    const bool vec_gla = MODE == TW_REC_GLA && sizeof(T) == 2 && (a.q_stride % 8) == 0 && (a.k_stride % 8) == 0
+                         && (reinterpret_cast<size_t>(a.q) % 16) == 0 && (reinterpret_cast<size_t>(a.k) % 16) == 0
+                         && (a.wpre_stride % 4) == 0 && (reinterpret_cast<size_t>(a.wpre) % 16) == 0
+                         && (reinterpret_cast<size_t>(a.p0) % 16) == 0;
+
     // ---- the rows of up to C tokens from t0 on, as fp32: rotation, scaling, decays and gates are evaluated here
     auto stage = [&](int t0, float* buf, int tid, int nthreads) {
         const int ct = min(C, len - t0);
@@ -170,6 +175,46 @@ linear_recurrence_kernel(RecArgs a) {
                     }
                     *reinterpret_cast<float4*>(sq + t * DKP + pad(i)) = qq;
                     *reinterpret_cast<float4*>(sk + t * DKP + pad(i)) = kk;
+                }
+                staged = true;
+            }
+        }
+        if constexpr (MODE == TW_REC_GLA && sizeof(T) == 2 && KS > 1 && DK % 8 == 0) {
+            if (vec_gla) {
+                // (the same arithmetic as one channel at a time.  The wkv rule's rows were staged this way too, and its
+                // 56 heads of 64 gained nothing: 528 us against 533 for 2,048 tokens; it keeps the loop below)
+                auto decay_of = [&](float x) { return expf(tw_logsigmoid(x) * a.cap); };
+                // bf16 rows whose heads start on 16-byte boundaries: four channels per load (8 bytes of q and of k, 16 of the
+                // projected decay and of its bias), and eight channels per thread and step where a head is wide enough to keep
+                // every staging thread busy that way; all of a thread's loads are under way before the first is used
+                constexpr int W = DK >= 128 ? 8 : 4, V = DK / W;
+                for (int e = tid; e < ct * V; e += nthreads) {
+                    const int t = e / V, i0 = W * (e - t * V);
+                    const size_t row = (size_t)(start + t0 + t);
+                    uint2 qraw[W / 4], kraw[W / 4];
+                    float4 dd[W / 4], bb[W / 4];
+#pragma unroll
+                    for (int g = 0; g < W / 4; ++g) {
+                        const int i = i0 + 4 * g;
+                        qraw[g] = *reinterpret_cast<const uint2*>(gq + row * a.q_stride + hq * DK + i);
+                        kraw[g] = *reinterpret_cast<const uint2*>(gk + row * a.k_stride + hq * DK + i);
+                        dd[g] = *reinterpret_cast<const float4*>(a.wpre + row * a.wpre_stride + h * DK + i);
+                        bb[g] = *reinterpret_cast<const float4*>(a.p0 + h * DK + i);
+                    }
+                    const float qs = a.q_scale, ks_ = a.k_scale;
+#pragma unroll
+                    for (int g = 0; g < W / 4; ++g) {
+                        const int i = i0 + 4 * g;
+                        const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&qraw[g]);
+                        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[g]);
+                        const float2 qa = __bfloat1622float2(q2[0]), qb = __bfloat1622float2(q2[1]);
+                        const float2 ka = __bfloat1622float2(k2[0]), kb = __bfloat1622float2(k2[1]);
+                        *reinterpret_cast<float4*>(sq + t * DKP + pad(i)) = make_float4(qa.x * qs, qa.y * qs, qb.x * qs, qb.y * qs);
+                        *reinterpret_cast<float4*>(sk + t * DKP + pad(i)) = make_float4(ka.x * ks_, ka.y * ks_, kb.x * ks_, kb.y * ks_);
+                        *reinterpret_cast<float4*>(sw + t * DKP + pad(i)) =
+                            make_float4(decay_of(dd[g].x + bb[g].x), decay_of(dd[g].y + bb[g].y), decay_of(dd[g].z + bb[g].z),
+                                        decay_of(dd[g].w + bb[g].w));
+                    }
                 }
                 staged = true;
             }
